@@ -1,0 +1,402 @@
+"""ctypes binding of ``libbittorch_b200.so`` (the C ABI declared in include/bittorch_b200.h).
+
+This module stands where the reference has its pybind11 extension ``bittorch._C``
+(csrc/bindings/bittorch_bindings.cpp:34-88): it exposes the same four callables
+(``dummy``, ``ternary_linear_forward``, ``ternary_linear_packed_forward``,
+``ternary_linear_tensor_core_forward``) with the argument checks of
+csrc/core/dispatch.cpp:52-142 raised as ``RuntimeError``, plus thin wrappers of the
+new entry points.  Importing it fails with ``ImportError`` when the library has not
+been built; nothing here computes on the CPU.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import Optional, Tuple
+
+import torch
+from torch import Tensor
+
+from . import _build
+
+BT_F32, BT_F16, BT_BF16 = 0, 1, 2
+GEMV_MAX_M = 16
+_DT = {torch.float32: BT_F32, torch.float16: BT_F16, torch.bfloat16: BT_BF16}
+
+_p = ctypes.c_void_p
+_i64 = ctypes.c_int64
+_int = ctypes.c_int
+_f32 = ctypes.c_float
+
+_SIGNATURES = {
+    "bt_version": ([], _int),
+    "bt_last_error": ([], ctypes.c_char_p),
+    "bt_device_status": ([_p, _p], _int),
+    "bt_dummy": ([_p, _p, ctypes.c_size_t, _p], _int),
+    "bt_quantize_pack": ([_p, _int, _i64, _i64, _i64, _f32, _p, _p, _p, _p, _p], _int),
+    "bt_pack_codes": ([_p, _i64, _i64, _p, _p], _int),
+    "bt_unpack_codes": ([_p, _i64, _i64, _p, _p], _int),
+    "bt_act_quant_i8": ([_p, _int, _i64, _i64, _i64, _p, _p, _p], _int),
+    "bt_tiled_bytes": ([_i64, _i64], ctypes.c_size_t),
+    "bt_retile_packed": ([_p, _i64, _i64, _p, _p], _int),
+    "bt_untile_packed": ([_p, _i64, _i64, _p, _p], _int),
+    "bt_gemv_packed_i8": ([_p, _p, _i64, _i64, _p, _i64, _p, _p, _p, _int, _i64, _p, _p], _int),
+    "bt_gemv_tiled_i8": ([_p, _p, _i64, _i64, _p, _i64, _p, _p, _p, _int, _i64, _p, _p], _int),
+    "bt_gemm_tiled_i8": ([_p, _p, _i64, _i64, _p, _i64, _p, _p, _p, _int, _i64, _p, _p], _int),
+    "bt_linear_unpacked": ([_p, _int, _i64, _i64, _p, _i64, _p, _p, _p, _p], _int),
+    "bt_linear_packed_float": ([_p, _int, _i64, _i64, _p, _i64, _p, _p, _p, _p], _int),
+}
+
+
+def _load() -> ctypes.CDLL:
+    path = os.environ.get("BITTORCH_B200_LIB", _build.LIB_PATH)
+    if not os.path.exists(path):
+        raise ImportError(
+            f"bittorch_b200: {path} has not been built; run `python -c 'import __graft_entry__ as g; g.build()'` "
+            "or `python -m bittorch_b200._build`"
+        )
+    try:
+        lib = ctypes.CDLL(path)
+    except OSError as exc:  # pragma: no cover - depends on the machine
+        raise ImportError(f"bittorch_b200: cannot load {path}: {exc}") from exc
+    for name, (argtypes, restype) in _SIGNATURES.items():
+        fn = getattr(lib, name)   # AttributeError -> a stale library; rebuild
+        fn.argtypes = argtypes
+        fn.restype = restype
+    return lib
+
+
+_lib = _load()
+LIB_PATH = _lib._name
+EXPORTED = tuple(_SIGNATURES)
+
+
+def version() -> int:
+    return int(_lib.bt_version())
+
+
+def _check(rc: int) -> None:
+    if rc != 0:
+        raise RuntimeError(_lib.bt_last_error().decode("utf-8", "replace") or f"bittorch_b200 error {rc}")
+
+
+def _ptr(t: Optional[Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _stream(t: Tensor):
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _dtype_code(t: Tensor, what: str) -> int:
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise RuntimeError(f"{what} must be float32, float16 or bfloat16, got {t.dtype}") from None
+
+
+def _f32vec(t: Optional[Tensor]) -> Optional[Tensor]:
+    """scale / bias cross the C ABI as contiguous float32 vectors."""
+    if t is None:
+        return None
+    return t.detach().to(torch.float32).contiguous()
+
+
+def device_status(device=None) -> int:
+    """Reads and clears the sticky device-side status word (synchronises the stream)."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    out = ctypes.c_int(0)
+    with torch.cuda.device(dev):
+        _check(_lib.bt_device_status(ctypes.byref(out), torch.cuda.current_stream(dev).cuda_stream))
+    return out.value
+
+
+# ---------------------------------------------------------------------------------------
+# New entry points (tensor-level wrappers; every tensor must live on a CUDA device)
+# ---------------------------------------------------------------------------------------
+
+def _require_cuda(*tensors: Tensor) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("All tensors must be CUDA")
+
+
+def quantize_pack(
+    weight: Tensor,
+    threshold_factor: float = 0.05,
+    want_packed: bool = True,
+    want_codes: bool = False,
+    want_tern: bool = False,
+) -> dict:
+    """Fused ternarize (+ pack) of a [N,K] master weight on the GPU.
+
+    Returns a dict with ``scale`` (float32 [N]) and, as requested, ``packed_T``
+    (uint8 [ceil(K/4),N]), ``codes`` (int8 [N,K]) and ``tern`` (weight dtype [N,K]).
+    """
+    _require_cuda(weight)
+    if weight.dim() != 2:
+        raise RuntimeError(f"weight must be 2D [N, K], got {weight.dim()}D")
+    w = weight.detach()
+    if w.stride(1) != 1 or w.stride(0) < w.shape[1]:
+        w = w.contiguous()
+    n, k = w.shape
+    if n == 0 or k == 0:
+        raise RuntimeError("weight is empty")
+    dev = w.device
+    out = {"scale": torch.empty(n, dtype=torch.float32, device=dev)}
+    if want_packed:
+        out["packed_T"] = torch.empty(((k + 3) // 4, n), dtype=torch.uint8, device=dev)
+    if want_codes:
+        out["codes"] = torch.empty((n, k), dtype=torch.int8, device=dev)
+    if want_tern:
+        out["tern"] = torch.empty((n, k), dtype=w.dtype, device=dev)
+    with torch.cuda.device(dev):
+        _check(_lib.bt_quantize_pack(
+            _ptr(w), _dtype_code(w, "weight"), n, k, w.stride(0), float(threshold_factor),
+            _ptr(out.get("packed_T")), _ptr(out["scale"]), _ptr(out.get("codes")), _ptr(out.get("tern")), _stream(w)))
+    return out
+
+
+def pack_codes(codes: Tensor) -> Tensor:
+    """int8 codes [N,K] -> public packed uint8 [ceil(K/4), N]."""
+    _require_cuda(codes)
+    codes = codes.contiguous()
+    n, k = codes.shape
+    out = torch.empty(((k + 3) // 4, n), dtype=torch.uint8, device=codes.device)
+    with torch.cuda.device(codes.device):
+        _check(_lib.bt_pack_codes(_ptr(codes), n, k, _ptr(out), _stream(codes)))
+    return out
+
+
+def unpack_codes(packed_T: Tensor, in_features: int) -> Tensor:
+    """public packed uint8 [ceil(K/4), N] -> int8 codes [N,K]."""
+    _require_cuda(packed_T)
+    packed_T = packed_T.contiguous()
+    n = packed_T.shape[1]
+    out = torch.empty((n, in_features), dtype=torch.int8, device=packed_T.device)
+    with torch.cuda.device(packed_T.device):
+        _check(_lib.bt_unpack_codes(_ptr(packed_T), n, in_features, _ptr(out), _stream(packed_T)))
+    return out
+
+
+def act_quant_i8(x2d: Tensor) -> Tuple[Tensor, Tensor]:
+    """Per-row int8 quantization of a [M,K] activation matrix -> (int8 [M,K], float32 [M])."""
+    _require_cuda(x2d)
+    if x2d.stride(1) != 1:
+        x2d = x2d.contiguous()
+    m, k = x2d.shape
+    xq = torch.empty((m, k), dtype=torch.int8, device=x2d.device)
+    sx = torch.empty((m,), dtype=torch.float32, device=x2d.device)
+    with torch.cuda.device(x2d.device):
+        _check(_lib.bt_act_quant_i8(_ptr(x2d), _dtype_code(x2d, "X"), m, k, x2d.stride(0), _ptr(xq), _ptr(sx), _stream(x2d)))
+    return xq, sx
+
+
+def tiled_bytes(in_features: int, out_features: int) -> int:
+    return int(_lib.bt_tiled_bytes(in_features, out_features))
+
+
+def retile(packed_T: Tensor, in_features: int) -> Tensor:
+    """Public packed buffer -> private tiled buffer (flat uint8)."""
+    _require_cuda(packed_T)
+    packed_T = packed_T.contiguous()
+    n = packed_T.shape[1]
+    out = torch.empty(tiled_bytes(in_features, n), dtype=torch.uint8, device=packed_T.device)
+    with torch.cuda.device(packed_T.device):
+        _check(_lib.bt_retile_packed(_ptr(packed_T), in_features, n, _ptr(out), _stream(packed_T)))
+    return out
+
+
+def untile(tiled: Tensor, in_features: int, out_features: int) -> Tensor:
+    """Private tiled buffer -> public packed uint8 [ceil(K/4), N]."""
+    _require_cuda(tiled)
+    out = torch.empty(((in_features + 3) // 4, out_features), dtype=torch.uint8, device=tiled.device)
+    with torch.cuda.device(tiled.device):
+        _check(_lib.bt_untile_packed(_ptr(tiled), in_features, out_features, _ptr(out), _stream(tiled)))
+    return out
+
+
+def _int_linear(fn, xq: Tensor, sx: Tensor, w: Tensor, k: int, n: int, scale: Tensor, bias: Optional[Tensor],
+                out_dtype: torch.dtype, want_acc: bool, out: Optional[Tensor] = None):
+    m = xq.shape[0]
+    y = torch.empty((m, n), dtype=out_dtype, device=xq.device) if out is None else out
+    acc = torch.empty((m, n), dtype=torch.int32, device=xq.device) if want_acc else None
+    with torch.cuda.device(xq.device):
+        _check(fn(_ptr(xq), _ptr(sx), m, k, _ptr(w), n, _ptr(scale), _ptr(bias), _ptr(y), _DT[out_dtype], y.stride(0),
+                  _ptr(acc), _stream(xq)))
+    return (y, acc) if want_acc else y
+
+
+def gemv_packed_i8(xq, sx, packed_T, in_features, scale, bias=None, out_dtype=torch.float32, want_acc=False, out=None):
+    """Decode-size integer linear on the public packed layout (M <= 16)."""
+    return _int_linear(_lib.bt_gemv_packed_i8, xq, sx, packed_T, in_features, packed_T.shape[1], scale, bias,
+                       out_dtype, want_acc, out)
+
+
+def gemv_tiled_i8(xq, sx, tiled, in_features, out_features, scale, bias=None, out_dtype=torch.float32, want_acc=False,
+                  out=None):
+    """Decode-size integer linear on the tiled layout (M <= 16): the bandwidth-bound fast path."""
+    return _int_linear(_lib.bt_gemv_tiled_i8, xq, sx, tiled, in_features, out_features, scale, bias, out_dtype,
+                       want_acc, out)
+
+
+def gemm_tiled_i8(xq, sx, tiled, in_features, out_features, scale, bias=None, out_dtype=torch.float32, want_acc=False,
+                  out=None):
+    """Prefill-size integer linear on the tiled layout (tcgen05 tensor cores)."""
+    return _int_linear(_lib.bt_gemm_tiled_i8, xq, sx, tiled, in_features, out_features, scale, bias, out_dtype,
+                       want_acc, out)
+
+
+def int8_linear_tiled(x2d: Tensor, tiled: Tensor, in_features: int, out_features: int, scale: Tensor,
+                      bias: Optional[Tensor]) -> Tensor:
+    """Activation quantizer + the kernel that fits M: GEMV for M <= 16, tcgen05 GEMM above.
+
+    K that is not a multiple of 16 cannot be described to the TMA engine; such ragged
+    shapes go through the decode kernel in chunks of 16 rows.
+    """
+    xq, sx = act_quant_i8(x2d)
+    m = x2d.shape[0]
+    if m <= GEMV_MAX_M:
+        return gemv_tiled_i8(xq, sx, tiled, in_features, out_features, scale, bias, x2d.dtype)
+    if in_features % 16 == 0:
+        return gemm_tiled_i8(xq, sx, tiled, in_features, out_features, scale, bias, x2d.dtype)
+    y = torch.empty((m, out_features), dtype=x2d.dtype, device=x2d.device)
+    for m0 in range(0, m, GEMV_MAX_M):
+        m1 = min(m, m0 + GEMV_MAX_M)
+        gemv_tiled_i8(xq[m0:m1], sx[m0:m1], tiled, in_features, out_features, scale, bias, x2d.dtype, out=y[m0:m1])
+    return y
+
+
+# ---------------------------------------------------------------------------------------
+# The four callables of the reference's extension module
+# ---------------------------------------------------------------------------------------
+
+def activation_mode() -> str:
+    """``int8`` (default: per-token int8 activations, integer contraction) or ``float``
+    (the reference's fp32-accumulate arithmetic), from ``BITTORCH_B200_ACT``."""
+    mode = os.environ.get("BITTORCH_B200_ACT", "int8").lower()
+    if mode not in ("int8", "float"):
+        raise RuntimeError(f"BITTORCH_B200_ACT must be 'int8' or 'float', got {mode!r}")
+    return mode
+
+
+def dummy(input: Tensor) -> Tensor:
+    """Clone of the input — replaces ``_C.dummy`` (csrc/core/dispatch.cpp:7-9).
+
+    CUDA tensors are copied by the library (``bt_dummy``); a CPU tensor, which the
+    reference's extension also accepts (tests/test_extension.py:43-58), is cloned by torch.
+    """
+    if not input.is_cuda:
+        return input.clone()
+    src = input.contiguous()
+    out = torch.empty_like(src)
+    with torch.cuda.device(src.device):
+        _check(_lib.bt_dummy(_ptr(src), _ptr(out), src.numel() * src.element_size(), _stream(src)))
+    return out
+
+
+def _check_common(X: Tensor, W: Tensor, scale: Tensor, bias: Optional[Tensor], n: int) -> None:
+    # Same order and messages as csrc/core/dispatch.cpp:58-79 / :112-133.
+    if scale.dim() != 1:
+        raise RuntimeError("scale must be 1D [N]")
+    if scale.shape[0] != n:
+        raise RuntimeError("scale size doesn't match N")
+    if bias is not None and (bias.dim() != 1 or bias.shape[0] != n):
+        raise RuntimeError("bias shape mismatch")
+    if not (X.is_cuda and W.is_cuda and scale.is_cuda):
+        raise RuntimeError("All tensors must be CUDA")
+
+
+def ternary_linear_forward(X: Tensor, W_tern: Tensor, scale: Tensor, bias: Optional[Tensor] = None) -> Tensor:
+    """Y = X @ (W_tern * scale).T + bias with int8 weights [N,K] and fp32 accumulation.
+
+    Replaces ``_C.ternary_linear_forward`` (csrc/core/dispatch.cpp:52-87).
+    """
+    if X.dim() < 1:
+        raise RuntimeError("X must have at least 1 dimension")
+    if X.numel() == 0:
+        raise RuntimeError("X is empty")
+    if W_tern.dim() != 2:
+        raise RuntimeError("W_tern must be 2D [N, K]")
+    if W_tern.dtype != torch.int8:
+        raise RuntimeError("W_tern must be int8")
+    k = X.shape[-1]
+    n, wk = W_tern.shape
+    if k != wk:
+        raise RuntimeError("input K doesn't match weight K")
+    _check_common(X, W_tern, scale, bias, n)
+    x2d = X.contiguous().reshape(-1, k)
+    w = W_tern.contiguous()
+    s32, b32 = _f32vec(scale), _f32vec(bias)
+    y = torch.empty((x2d.shape[0], n), dtype=X.dtype, device=X.device)
+    with torch.cuda.device(X.device):
+        _check(_lib.bt_linear_unpacked(_ptr(x2d), _dtype_code(x2d, "X"), x2d.shape[0], k, _ptr(w), n, _ptr(s32),
+                                       _ptr(b32), _ptr(y), _stream(x2d)))
+    return y.reshape(*X.shape[:-1], n)
+
+
+def _packed_checks(X: Tensor, W_T: Tensor, scale: Tensor, bias: Optional[Tensor], in_features: int) -> Tuple[int, int]:
+    if X.dim() < 1:
+        raise RuntimeError("X must have at least 1 dimension")
+    if X.numel() == 0:
+        raise RuntimeError("X is empty")
+    if W_T.dim() != 2:
+        raise RuntimeError("W_T must be 2D [K_bytes, N]")
+    if W_T.dtype != torch.uint8:
+        raise RuntimeError("W_T must be uint8")
+    k = X.shape[-1]
+    k_bytes, n = W_T.shape
+    if k != in_features:
+        raise RuntimeError("input K doesn't match in_features")
+    if k_bytes != (in_features + 3) // 4:
+        raise RuntimeError("K_bytes doesn't match ceil(K/4)")
+    _check_common(X, W_T, scale, bias, n)
+    return k, n
+
+
+def _packed_forward(X: Tensor, W_T: Tensor, scale: Tensor, bias: Optional[Tensor], k: int, n: int, mode: str) -> Tensor:
+    x2d = X.contiguous().reshape(-1, k)
+    w = W_T.contiguous()
+    s32, b32 = _f32vec(scale), _f32vec(bias)
+    m = x2d.shape[0]
+    if mode == "float":
+        y = torch.empty((m, n), dtype=X.dtype, device=X.device)
+        with torch.cuda.device(X.device):
+            _check(_lib.bt_linear_packed_float(_ptr(x2d), _dtype_code(x2d, "X"), m, k, _ptr(w), n, _ptr(s32), _ptr(b32),
+                                               _ptr(y), _stream(x2d)))
+    elif m <= GEMV_MAX_M:
+        xq, sx = act_quant_i8(x2d)
+        y = gemv_packed_i8(xq, sx, w, k, s32, b32, X.dtype)
+    else:
+        y = int8_linear_tiled(x2d, retile(w, k), k, n, s32, b32)
+    return y.reshape(*X.shape[:-1], n)
+
+
+def ternary_linear_packed_forward(X: Tensor, W_T: Tensor, scale: Tensor, bias: Optional[Tensor] = None,
+                                  in_features: Optional[int] = None) -> Tensor:
+    """Packed ternary linear on the public [ceil(K/4), N] buffer.
+
+    Replaces ``_C.ternary_linear_packed_forward`` (csrc/core/dispatch.cpp:105-142).  Small
+    batches run the decode kernel on the buffer as it is; larger ones re-tile it for the
+    tensor-core kernel (modules cache that copy, this stateless call cannot).
+    """
+    if in_features is None:
+        raise TypeError("ternary_linear_packed_forward() missing required argument: 'in_features'")
+    k, n = _packed_checks(X, W_T, scale, bias, int(in_features))
+    return _packed_forward(X, W_T, scale, bias, k, n, activation_mode())
+
+
+def ternary_linear_tensor_core_forward(X: Tensor, W_T: Tensor, scale: Tensor, bias: Optional[Tensor] = None,
+                                       in_features: Optional[int] = None, version: int = 1) -> Tensor:
+    """Replaces ``_C.ternary_linear_tensor_core_forward``
+    (csrc/kernels/ternary_gemm_tensor_core.cu:663-727): version 1 = float compute,
+    version 2 = int8 activations on the tensor cores (per-row activation scales)."""
+    if X.dim() != 2:
+        raise RuntimeError("X must be 2D")
+    if version not in (1, 2):
+        raise RuntimeError("version must be 1 (V1 float) or 2 (V2 mma.sync)")
+    if in_features is None:
+        in_features = X.shape[-1]
+    k, n = _packed_checks(X, W_T, scale, bias, int(in_features))
+    return _packed_forward(X, W_T, scale, bias, k, n, "float" if version == 1 else "int8")

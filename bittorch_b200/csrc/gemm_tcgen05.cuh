@@ -1,0 +1,419 @@
+// Prefill-size packed ternary linear on int8 activations: tcgen05 (5th-gen tensor core)
+// GEMM with accumulators in tensor memory.
+//
+// Persistent kernel, one CTA per SM, output tile 128 (rows of X) x 256 (output columns),
+// K consumed in blocks of 128.  Warp roles:
+//   warp 0       producer: TMA tensor load of the int8 activation tile (128 x 128 B,
+//                128-byte swizzle) and 1-D bulk copies of the 2-bit weight tiles (8 KB)
+//   warp 1       MMA issuer: 4 x tcgen05.mma.kind::i8 (128x256x32) per K block, commits
+//                free the stage / publish the accumulator
+//   warps 2-5    epilogue: tcgen05.ld of the int32 accumulators, un-scale, dequantise, store
+//   warps 6-13   unpack: 2-bit tiles -> signed int8 in the K-major 128-byte-swizzled B tile
+// The unpacked weight of plane i (columns 16i..16i+15 of each 64-column block) is stored as
+// t * 4^i (one mask, one subtract, one xor per four weights); the epilogue shifts it back.
+// Accumulators are double-buffered in the 512 TMEM columns so the epilogue of one tile
+// overlaps the main loop of the next.
+// Algorithmic work per call: 2*M*N*K integer ops.
+#pragma once
+
+#include <cuda.h>   // CUtensorMap types only; the encoder is looked up at run time
+
+#include "common.cuh"
+#include "retile.cuh"
+
+namespace bt {
+
+constexpr int GM_BM = 128;
+constexpr int GM_BN = 256;
+constexpr int GM_BK = 128;                       // bytes = int8 elements per K block
+constexpr int GM_STAGES = 3;
+constexpr int GM_A_BYTES = GM_BM * GM_BK;        // 16 KB
+constexpr int GM_B_BYTES = GM_BN * GM_BK;        // 32 KB
+constexpr int GM_P_BYTES = (GM_BN / TILE_N) * (GM_BK / TILE_K) * TILE_BYTES;   // 8 KB of packed tiles
+constexpr int GM_UNPACK_WARPS = 8;
+constexpr int GM_EPI_WARPS = 4;
+constexpr int GM_THREADS = (2 + GM_EPI_WARPS + GM_UNPACK_WARPS) * 32;          // 448
+constexpr int GM_TMEM_COLS = 512;
+constexpr size_t GM_SMEM_BYTES = 1024 /*alignment slack*/ + GM_STAGES * (GM_A_BYTES + GM_B_BYTES + GM_P_BYTES) + 256;
+
+struct GemmParams {
+    const uint8_t* tiled;
+    const float* sx;
+    const float* scale;
+    const float* bias;
+    void* Y;
+    int32_t* acc_out;
+    int64_t ldy;
+    int M, K, N;
+    int KT;        // 32-wide k tiles in the tiled layout
+    int NB;        // 64-wide column blocks in the tiled layout
+    int y_dtype;
+};
+
+// ---- tcgen05 / TMA PTX wrappers ----------------------------------------------------------
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Arrives on the mbarrier once every MMA issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, int (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows 128 B apart,
+// 8-row groups 1024 B apart (stride byte offset), descriptor version 1 (sm_100).
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr & 0x3ffffu) >> 4);       // start address
+    d |= static_cast<uint64_t>(1) << 16;                            // leading byte offset (unused for swizzled K-major)
+    d |= static_cast<uint64_t>(1024 >> 4) << 32;                    // stride byte offset
+    d |= static_cast<uint64_t>(1) << 46;                            // version
+    d |= static_cast<uint64_t>(2) << 61;                            // SWIZZLE_128B
+    return d;
+}
+// Instruction descriptor: D = s32, A = B = s8, both K-major, M = 128, N = GM_BN.
+constexpr uint32_t GM_IDESC = (2u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(GM_BN >> 3) << 17) |
+                              (static_cast<uint32_t>(GM_BM >> 4) << 24);
+
+// Bounded mbarrier wait that also gives up when another role has already failed.
+__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    for (uint32_t i = 0; i < (1u << 22); ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 255u) == 255u && *abort_flag) return false;
+    }
+    report_wait_timeout();
+    *abort_flag = 1;
+    return false;
+}
+
+__global__ void __launch_bounds__(GM_THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const GemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* s_a = smem;
+    uint8_t* s_b = s_a + GM_STAGES * GM_A_BYTES;
+    uint8_t* s_p = s_b + GM_STAGES * GM_B_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(s_p + GM_STAGES * GM_P_BYTES);
+    uint64_t* full_load = bars;                      // [GM_STAGES] producer -> unpack, MMA
+    uint64_t* full_b = bars + GM_STAGES;             // [GM_STAGES] unpack -> MMA
+    uint64_t* empty = bars + 2 * GM_STAGES;          // [GM_STAGES] MMA -> producer
+    uint64_t* tmem_full = bars + 3 * GM_STAGES;      // [2] MMA -> epilogue
+    uint64_t* tmem_empty = tmem_full + 2;            // [2] epilogue -> MMA
+    uint32_t* s_tmem = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+    __shared__ int s_abort_storage;
+    volatile int* s_abort = &s_abort_storage;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m_tiles = (p.M + GM_BM - 1) / GM_BM;
+    const int n_tiles = (p.N + GM_BN - 1) / GM_BN;
+    const int total_tiles = m_tiles * n_tiles;
+    const int k_blocks = (p.K + GM_BK - 1) / GM_BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < GM_STAGES; ++s) {
+            mbar_init(&full_load[s], 1);
+            mbar_init(&full_b[s], GM_UNPACK_WARPS);
+            mbar_init(&empty[s], 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(&tmem_full[a], 1);
+            mbar_init(&tmem_empty[a], GM_EPI_WARPS);
+        }
+        s_abort_storage = 0;
+        mbar_fence_init();
+    }
+    if (warp == 2) tmem_alloc(s_tmem, GM_TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *s_tmem;
+    pdl_launch_dependents();
+    pdl_wait();   // activations (and their scales) come from the preceding kernel
+
+    if (warp == 0) {
+        // ================= producer =================
+        if (lane == 0) {
+            uint32_t it = 0;
+            for (int tile = blockIdx.x; tile < total_tiles && !*s_abort; tile += gridDim.x) {
+                const int mt = tile % m_tiles, nt = tile / m_tiles;
+                const int nb0 = nt * (GM_BN / TILE_N);
+                const int nb_valid = min(GM_BN / TILE_N, p.NB - nb0);
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const int s = it % GM_STAGES;
+                    if (!wait_or_abort(&empty[s], ((it / GM_STAGES) & 1) ^ 1, s_abort)) break;
+                    const int kt0 = kb * (GM_BK / TILE_K);
+                    const int kt_valid = min(GM_BK / TILE_K, p.KT - kt0);
+                    const uint32_t p_bytes = static_cast<uint32_t>(kt_valid) * TILE_BYTES;
+                    mbar_expect_tx(&full_load[s], GM_A_BYTES + static_cast<uint32_t>(nb_valid) * p_bytes);
+                    tma_load_2d(s_a + s * GM_A_BYTES, &map_x, kb * GM_BK, mt * GM_BM, &full_load[s]);
+                    for (int j = 0; j < nb_valid; ++j)
+                        bulk_g2s(s_p + s * GM_P_BYTES + j * (GM_BK / TILE_K) * TILE_BYTES,
+                                 p.tiled + (static_cast<int64_t>(nb0 + j) * p.KT + kt0) * TILE_BYTES, p_bytes, &full_load[s]);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ================= MMA issuer =================
+        if (lane == 0) {
+            uint32_t it = 0, tcount = 0;
+            for (int tile = blockIdx.x; tile < total_tiles && !*s_abort; tile += gridDim.x, ++tcount) {
+                const uint32_t a = tcount & 1;
+                if (!wait_or_abort(&tmem_empty[a], ((tcount >> 1) & 1) ^ 1, s_abort)) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + a * GM_BN;
+                bool ok = true;
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const int s = it % GM_STAGES;
+                    const uint32_t ph = (it / GM_STAGES) & 1;
+                    if (!wait_or_abort(&full_load[s], ph, s_abort) || !wait_or_abort(&full_b[s], ph, s_abort)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint64_t da = umma_desc_sw128(smem_u32(s_a + s * GM_A_BYTES));
+                    const uint64_t db = umma_desc_sw128(smem_u32(s_b + s * GM_B_BYTES));
+#pragma unroll
+                    for (int k = 0; k < GM_BK / 32; ++k)   // +32 bytes along K = +2 in the (>>4) address field
+                        umma_i8(d_tmem, da + 2 * k, db + 2 * k, GM_IDESC, (kb > 0 || k > 0) ? 1u : 0u);
+                    umma_commit(&empty[s]);
+                }
+                if (!ok) break;
+                umma_commit(&tmem_full[a]);
+            }
+        }
+    } else if (warp < 2 + GM_EPI_WARPS) {
+        // ================= epilogue =================
+        const int lq = warp & 3;                       // TMEM lane quarter this warp may access
+        uint32_t tcount = 0;
+        for (int tile = blockIdx.x; tile < total_tiles && !*s_abort; tile += gridDim.x, ++tcount) {
+            const int mt = tile % m_tiles, nt = tile / m_tiles;
+            const uint32_t a = tcount & 1;
+            if (!wait_or_abort(&tmem_full[a], (tcount >> 1) & 1, s_abort)) break;
+            tc_fence_after();
+            const int m = mt * GM_BM + lq * 32 + lane;
+            const float sxm = (m < p.M) ? p.sx[m] : 0.0f;
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(lq * 32) << 16) + a * GM_BN;
+#pragma unroll 1
+            for (int c0 = 0; c0 < GM_BN; c0 += 32) {
+                int v[32];
+                tmem_ld_32x32b_x32(taddr + c0, v);
+                tmem_ld_wait();
+                if (c0 + 32 == GM_BN) {
+                    // accumulator fully read: hand the TMEM buffer back before the stores
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&tmem_empty[a]);
+                }
+                const int n0 = nt * GM_BN + c0;
+                if (m < p.M && n0 < p.N) {
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) {
+                        const int plane = ((c0 + c) % TILE_N) / 16;   // c0 is a multiple of 32, so this folds per c
+                        v[c] >>= 2 * plane;
+                    }
+                    if (p.acc_out != nullptr) {
+#pragma unroll
+                        for (int c = 0; c < 32; ++c)
+                            if (n0 + c < p.N) p.acc_out[static_cast<int64_t>(m) * p.N + n0 + c] = v[c];
+                    }
+                    float y[32];
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) {
+                        const int n = min(n0 + c, p.N - 1);
+                        y[c] = dequant(v[c], sxm, __ldg(p.scale + n), p.bias ? __ldg(p.bias + n) : 0.0f, p.bias != nullptr);
+                    }
+                    const int64_t base = static_cast<int64_t>(m) * p.ldy + n0;
+                    const bool full = (n0 + 32 <= p.N);
+                    if (p.y_dtype == BT_F32) {
+                        float* out = reinterpret_cast<float*>(p.Y) + base;
+                        if (full && aligned(out, 16)) {
+#pragma unroll
+                            for (int c = 0; c < 32; c += 4)
+                                *reinterpret_cast<float4*>(out + c) = make_float4(y[c], y[c + 1], y[c + 2], y[c + 3]);
+                        } else {
+#pragma unroll
+                            for (int c = 0; c < 32; ++c)
+                                if (n0 + c < p.N) out[c] = y[c];
+                        }
+                    } else {
+                        uint16_t* out = reinterpret_cast<uint16_t*>(p.Y) + base;
+                        uint32_t pk[16];
+#pragma unroll
+                        for (int c = 0; c < 32; c += 2) {
+                            if (p.y_dtype == BT_F16) {
+                                __half2 h = __floats2half2_rn(y[c], y[c + 1]);
+                                pk[c / 2] = *reinterpret_cast<uint32_t*>(&h);
+                            } else {
+                                __nv_bfloat162 h = __floats2bfloat162_rn(y[c], y[c + 1]);
+                                pk[c / 2] = *reinterpret_cast<uint32_t*>(&h);
+                            }
+                        }
+                        if (full && aligned(out, 16)) {
+#pragma unroll
+                            for (int c = 0; c < 16; c += 4)
+                                *reinterpret_cast<uint4*>(out + 2 * c) = make_uint4(pk[c], pk[c + 1], pk[c + 2], pk[c + 3]);
+                        } else {
+#pragma unroll
+                            for (int c = 0; c < 32; ++c)
+                                if (n0 + c < p.N) out[c] = static_cast<uint16_t>(pk[c / 2] >> (16 * (c & 1)));
+                        }
+                    }
+                }
+            }
+        }
+    } else {
+        // ================= unpack: 2-bit tiles -> signed int8, K-major, 128-byte swizzle =================
+        const int utid = threadIdx.x - (2 + GM_EPI_WARPS) * 32;   // 0..255
+        const int uwarp = utid >> 5;
+        const int g = lane >> 2, t = lane & 3;
+        uint32_t it = 0;
+        for (int tile = blockIdx.x; tile < total_tiles && !*s_abort; tile += gridDim.x) {
+            bool ok = true;
+            for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                const int s = it % GM_STAGES;
+                if (!wait_or_abort(&full_load[s], (it / GM_STAGES) & 1, s_abort)) { ok = false; break; }
+                const uint8_t* pk = s_p + s * GM_P_BYTES;
+                uint8_t* bt = s_b + s * GM_B_BYTES;
+                // 16 packed tiles (4 column blocks x 4 k tiles) per stage, 2 per warp
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    const int tix = uwarp * 2 + u;
+                    const int nbl = tix >> 2, ktl = tix & 3;
+                    const uint4 wv = *reinterpret_cast<const uint4*>(pk + tix * TILE_BYTES + lane * 16);
+                    const uint32_t w[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            // field (t+1)*4^i  ->  signed byte t*4^i, without borrows between bytes
+                            uint32_t v = (w[q] & (0x03030303u << (2 * i))) | 0x80808080u;
+                            v = (v - (0x01010101u << (2 * i))) ^ 0x80808080u;
+                            const int row = TILE_N * nbl + 16 * i + g + 8 * (q & 1);
+                            const int chunk = (2 * ktl + (q >> 1)) ^ (row & 7);
+                            *reinterpret_cast<uint32_t*>(bt + (row >> 3) * 1024 + (row & 7) * 128 + chunk * 16 + 4 * t) = v;
+                        }
+                    }
+                }
+                fence_proxy_async_smem();   // generic-proxy writes -> visible to the tensor core (async proxy)
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&full_b[s]);
+            }
+            if (!ok) break;
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 2) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, GM_TMEM_COLS);
+    }
+}
+
+// ---- host side ------------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_tiled() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    return fn;
+}
+
+}  // namespace bt
+
+extern "C" int bt_gemm_tiled_i8(const int8_t* Xq, const float* sx, int64_t M, int64_t K, const uint8_t* tiled, int64_t N,
+                                const float* scale, const float* bias, void* Y, int y_dtype, int64_t ldy,
+                                int32_t* acc_out, void* stream) {
+    using namespace bt;
+    BT_REQUIRE(Xq && sx && tiled && scale && Y, "bt_gemm_tiled_i8: NULL pointer");
+    BT_REQUIRE(M > 0 && K > 0 && N > 0, "bt_gemm_tiled_i8: X is empty or weight is empty");
+    BT_REQUIRE(valid_dtype(y_dtype), "bt_gemm_tiled_i8: unknown output dtype %d", y_dtype);
+    BT_REQUIRE(ldy >= N, "bt_gemm_tiled_i8: output row stride %lld < N %lld", (long long)ldy, (long long)N);
+    BT_REQUIRE(aligned(tiled, 16) && aligned(Xq, 16), "bt_gemm_tiled_i8: Xq and tiled weights must be 16-byte aligned");
+    BT_UNSUPPORTED_IF(K % 16 != 0, "bt_gemm_tiled_i8: K=%lld must be a multiple of 16 (TMA row pitch)", (long long)K);
+    BT_UNSUPPORTED_IF(K > BT_MAX_K || N > (int64_t{1} << 30) || M > (int64_t{1} << 30), "bt_gemm_tiled_i8: shape too large");
+
+    EncodeTiledFn encode = get_encode_tiled();
+    if (encode == nullptr) {
+        set_error("bt_gemm_tiled_i8: cuTensorMapEncodeTiled is not available from the driver");
+        return BT_ERR_CUDA;
+    }
+    CUtensorMap map;
+    const cuuint64_t gdim[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(M)};
+    const cuuint64_t gstride[1] = {static_cast<cuuint64_t>(K)};
+    const cuuint32_t box[2] = {GM_BK, GM_BM};
+    const cuuint32_t estride[2] = {1, 1};
+    CUresult cr = encode(&map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t*>(Xq), gdim, gstride, box, estride,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (cr != CUDA_SUCCESS) {
+        set_error("bt_gemm_tiled_i8: cuTensorMapEncodeTiled failed with code %d", static_cast<int>(cr));
+        return BT_ERR_CUDA;
+    }
+
+    GemmParams p;
+    p.tiled = tiled; p.sx = sx; p.scale = scale; p.bias = bias; p.Y = Y; p.acc_out = acc_out; p.ldy = ldy;
+    p.M = static_cast<int>(M); p.K = static_cast<int>(K); p.N = static_cast<int>(N);
+    p.KT = static_cast<int>(ceil_div<int64_t>(K, TILE_K));
+    p.NB = static_cast<int>(ceil_div<int64_t>(N, TILE_N));
+    p.y_dtype = y_dtype;
+
+    const int64_t tiles = ceil_div<int64_t>(M, GM_BM) * ceil_div<int64_t>(N, GM_BN);
+    const unsigned grid = static_cast<unsigned>(std::min<int64_t>(tiles, sm_count()));
+    BT_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    static_cast<int>(GM_SMEM_BYTES)));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(GM_THREADS);
+    cfg.dynamicSmemBytes = GM_SMEM_BYTES;
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attrs[1];
+    attrs[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attrs;
+    cfg.numAttrs = 1;
+    BT_CUDA_OK(cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel, map, p));
+    return BT_OK;
+}

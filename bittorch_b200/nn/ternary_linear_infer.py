@@ -1,0 +1,99 @@
+"""TernaryLinearInference — packed-weight inference module
+(bittorch/nn/ternary_linear_infer.py).
+
+Buffers keep the reference's names, dtypes and shapes (``weight_packed`` uint8
+[ceil(K/4), N], ``scale`` [N], ``bias`` [N]) so its checkpoints load unchanged.  The
+forward runs on a privately re-tiled copy of ``weight_packed`` that is rebuilt whenever
+the buffer changes and is never serialized.
+"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.nn as nn
+from torch import Tensor
+
+from .._ext import require_cuda_tensor, require_ext
+from ..quant.ternary_packed import pack_ternary_transposed
+
+
+class TernaryLinearInference(nn.Module):
+    """Inference-only linear layer on 2-bit packed ternary weights (no master weights,
+    no autograd).  Constructor as in bittorch/nn/ternary_linear_infer.py:46-76."""
+
+    def __init__(self, in_features: int, out_features: int, weight_packed: Tensor, scale: Tensor,
+                 bias: Optional[Tensor] = None):
+        super().__init__()
+        self.in_features = in_features
+        self.out_features = out_features
+        self.register_buffer("weight_packed", weight_packed)
+        self.register_buffer("scale", scale)
+        self.register_buffer("bias", bias if bias is not None else None)
+        self.requires_grad_(False)
+        self._derived_key = None
+        self._tiled: Optional[Tensor] = None
+        self._scale32: Optional[Tensor] = None
+        self._bias32: Optional[Tensor] = None
+
+    def _derived(self):
+        """Tiled weights and float32 scale/bias, rebuilt when a buffer was replaced or written."""
+        wp, sc, b = self.weight_packed, self.scale, self.bias
+        key = (wp.data_ptr(), wp._version, sc.data_ptr(), sc._version,
+               None if b is None else (b.data_ptr(), b._version))
+        if key != self._derived_key:
+            C = require_ext()
+            self._tiled = C.retile(wp, self.in_features)
+            self._scale32 = sc.to(torch.float32).contiguous()
+            self._bias32 = None if b is None else b.to(torch.float32).contiguous()
+            self._derived_key = key
+        return self._tiled, self._scale32, self._bias32
+
+    def forward(self, x: Tensor) -> Tensor:
+        """x: (*, in_features) CUDA tensor -> (*, out_features), dtype of x."""
+        require_cuda_tensor(x, "input")
+        C = require_ext()
+        if x.shape[-1] != self.in_features:
+            raise RuntimeError("input K doesn't match in_features")
+        if x.numel() == 0:
+            raise RuntimeError("X is empty")
+        if C.activation_mode() == "float":
+            return C.ternary_linear_packed_forward(x, self.weight_packed, self.scale, self.bias, self.in_features)
+        tiled, s32, b32 = self._derived()
+        x2d = x.contiguous().reshape(-1, self.in_features)
+        y = C.int8_linear_tiled(x2d, tiled, self.in_features, self.out_features, s32, b32)
+        return y.reshape(*x.shape[:-1], self.out_features)
+
+    def extra_repr(self) -> str:
+        packed_bytes = self.weight_packed.numel()
+        reduction = (self.out_features * self.in_features * 4) / (packed_bytes + self.scale.numel() * 2)
+        return (f"in_features={self.in_features}, out_features={self.out_features}, bias={self.bias is not None}, "
+                f"packed_bytes={packed_bytes}, reduction={reduction:.1f}x")
+
+    @classmethod
+    def from_unpacked(cls, w_tern: Tensor, scale: Tensor, bias: Optional[Tensor] = None) -> "TernaryLinearInference":
+        """Build from ternary weights [N,K] (values -1/0/+1) and per-channel scales
+        (bittorch/nn/ternary_linear_infer.py:120-152)."""
+        out_features, in_features = w_tern.shape
+        weight_packed, _ = pack_ternary_transposed(w_tern)
+        return cls(in_features, out_features, weight_packed, scale, bias)
+
+    @property
+    def packed_size_bytes(self) -> int:
+        return self.weight_packed.numel()
+
+    @property
+    def effective_bits_per_weight(self) -> float:
+        total_bits = self.weight_packed.numel() * 8 + self.scale.numel() * 16
+        return total_bits / (self.out_features * self.in_features)
+
+
+def create_ternary_linear_inference(in_features: int, out_features: int, weight: Tensor, bias: Optional[Tensor] = None,
+                                    threshold_factor: float = 0.05) -> TernaryLinearInference:
+    """Quantize + pack full-precision weights [N,K] in one fused kernel and wrap them
+    (bittorch/nn/ternary_linear_infer.py:163-193)."""
+    from ..quant.ternary_packed import quantize_pack_transposed
+
+    packed_T, scale, _ = quantize_pack_transposed(weight, threshold_factor)
+    return TernaryLinearInference(in_features, out_features, packed_T, scale, bias)

@@ -1,0 +1,178 @@
+/*
+ * bittorch_b200 — C ABI of the B200 (sm_100a) ternary linear backend.
+ *
+ * This header is the drop-in boundary: a torch-free shared library
+ * (libbittorch_b200.so) whose entry points take raw device pointers, explicit
+ * sizes and a CUDA stream.  It replaces the reference's pybind11 extension
+ * `bittorch._C` (csrc/bindings/bittorch_bindings.cpp:34-88) and the host dispatch
+ * behind it (csrc/core/dispatch.cpp).
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer unless said otherwise;
+ *   - `stream` is a cudaStream_t passed as void* (NULL = legacy default stream);
+ *     all work is enqueued on it and nothing synchronises unless stated;
+ *   - return value: BT_OK (0) or a BT_ERR_* code; bt_last_error() then returns a
+ *     human-readable message for the calling thread;
+ *   - no entry point allocates or frees device memory; outputs and workspaces
+ *     are the caller's (sizes from the bt_*_bytes helpers);
+ *   - nothing throws or aborts across this boundary, and no kernel traps: a
+ *     device-side wait that runs out records a code readable with
+ *     bt_device_status().
+ *   - scale / bias vectors are always float32 on this side of the boundary; the
+ *     Python layer converts the (tiny) [N] vectors when the reference API hands
+ *     them over in fp16 / bf16.
+ */
+#ifndef BITTORCH_B200_H
+#define BITTORCH_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define BT_OK 0
+#define BT_ERR_INVALID 1      /* bad argument (shape, alignment, NULL, dtype) */
+#define BT_ERR_CUDA 2         /* a CUDA runtime call or launch failed */
+#define BT_ERR_UNSUPPORTED 3  /* valid request outside the kernel's limits */
+#define BT_ERR_DEVICE_WAIT 4  /* a bounded device-side wait ran out */
+
+/* Element types of activations / master weights / outputs. */
+#define BT_F32 0
+#define BT_F16 1
+#define BT_BF16 2
+
+/* Largest M handled by the decode (GEMV) kernels. */
+#define BT_GEMV_MAX_M 16
+/* Largest K of the integer kernels: keeps 128*127*K inside int32. */
+#define BT_MAX_K 131072
+
+/* Library version, major*10000 + minor*100 + patch. */
+int bt_version(void);
+
+/* Message for the last non-zero return on the calling thread ("" if none). */
+const char* bt_last_error(void);
+
+/*
+ * Reads (and clears) the sticky device-side status word of the current device:
+ * 0, or BT_ERR_DEVICE_WAIT if some kernel gave up on a bounded wait since the
+ * last call.  Synchronises `stream`.
+ */
+int bt_device_status(int* status_host, void* stream);
+
+/*
+ * Device-to-device clone of `bytes` bytes.
+ * Replaces `_C.dummy` (csrc/core/dispatch.cpp:7-9).
+ */
+int bt_dummy(const void* src, void* dst, size_t bytes, void* stream);
+
+/*
+ * Fused weight ternarizer + 2-bit packer.
+ *   scale[n] = clamp(max_k |W[n,k]|, 1e-8);  thr = threshold_factor * scale[n];
+ *   code     = |W| > thr ? sign(W) : 0;      byte[kb,n] = codes of W[n,4kb..4kb+3]
+ * (0 -> 00, +1 -> 01, -1 -> 10, K padded with zeros), arithmetic in W's dtype.
+ * Replaces bittorch.quant.ternary_quantize (bittorch/quant/ternary.py:100-150)
+ * followed by pack_ternary_transposed (bittorch/quant/ternary_packed.py:174-206).
+ *
+ * W         [N,K] row-major with row stride ldw (elements), dtype w_dtype
+ * packed_T  uint8 [ceil(K/4), N]            (may be NULL)
+ * scale     float32 [N]                     (values are exact widenings of w_dtype)
+ * codes     int8 [N,K] in {-1,0,+1}         (may be NULL)
+ * tern      [N,K] contiguous, dtype w_dtype, values -1/0/+1 (may be NULL);
+ *           this is what TernaryLinear.get_quantized_weight() returns
+ *           (bittorch/nn/ternary_linear.py:227-242).
+ */
+int bt_quantize_pack(const void* W, int w_dtype, int64_t N, int64_t K, int64_t ldw,
+                     float threshold_factor, uint8_t* packed_T, float* scale,
+                     int8_t* codes, void* tern, void* stream);
+
+/*
+ * 2-bit packer / unpacker for already-ternary weights.
+ * Replace pack_ternary_transposed / unpack_ternary_transposed
+ * (bittorch/quant/ternary_packed.py:174-223).  codes: int8 [N,K].  The reserved
+ * bit pattern 11 decodes to 0 (ternary_packed.py:112-115).
+ */
+int bt_pack_codes(const int8_t* codes, int64_t N, int64_t K, uint8_t* packed_T, void* stream);
+int bt_unpack_codes(const uint8_t* packed_T, int64_t N, int64_t K, int8_t* codes, void* stream);
+
+/*
+ * Per-token int8 activation quantizer (one scale per row of X):
+ *   s = max|x| > 1e-6 ? max|x|/127 : 1;  q = clamp(roundf(x * (1/s)), -127, 127)
+ * Replaces the in-kernel quantizer of the reference's integer kernel
+ * (csrc/kernels/ternary_gemm_tensor_core.cu:343-347, 424-459), applied per row as
+ * that file's header specifies (:16-18).
+ * X [M,K] row stride ldx, dtype x_dtype; Xq int8 [M,K]; sx float32 [M].
+ */
+int bt_act_quant_i8(const void* X, int x_dtype, int64_t M, int64_t K, int64_t ldx,
+                    int8_t* Xq, float* sx, void* stream);
+
+/*
+ * Private streaming layout of the packed weights ("tiled"): still 2 bits per
+ * weight, re-ordered into 512-byte tiles of 64 output columns x 32 inputs so that
+ * one 16-byte load per lane is a ready-made tensor-core operand.  It is a derived
+ * cache of the public [ceil(K/4),N] buffer and round-trips to it bit for bit.
+ * (No counterpart in the reference; the public buffer stays the wire format of
+ * TernaryLinearInference.weight_packed, bittorch/nn/ternary_linear_infer.py:68-73.)
+ */
+size_t bt_tiled_bytes(int64_t K, int64_t N);
+int bt_retile_packed(const uint8_t* packed_T, int64_t K, int64_t N, uint8_t* tiled, void* stream);
+int bt_untile_packed(const uint8_t* tiled, int64_t K, int64_t N, uint8_t* packed_T, void* stream);
+
+/*
+ * Decode-size (M <= BT_GEMV_MAX_M) packed ternary linear on int8 activations:
+ *   acc[m,n] = sum_k Xq[m,k] * T[n,k]            (int32, exact)
+ *   Y[m,n]   = (float(acc) * sx[m]) * scale[n] + bias[n]
+ * bt_gemv_packed_i8 reads the public [ceil(K/4),N] buffer, bt_gemv_tiled_i8 the
+ * tiled one (the bandwidth-bound fast path).  Both replace
+ * ternary_linear_packed_forward for small batches
+ * (csrc/core/dispatch.cpp:105-142; csrc/kernels/ternary_gemm_production.cu:53-142)
+ * with the integer arithmetic of csrc/kernels/ternary_gemm_tensor_core.cu:349-657.
+ *
+ * Xq int8 [M,K] contiguous; sx float32 [M]; scale float32 [N]; bias float32 [N] or NULL;
+ * Y [M,N] row stride ldy, dtype y_dtype; acc_out int32 [M,N] or NULL (parity checks).
+ */
+int bt_gemv_packed_i8(const int8_t* Xq, const float* sx, int64_t M, int64_t K,
+                      const uint8_t* packed_T, int64_t N, const float* scale, const float* bias,
+                      void* Y, int y_dtype, int64_t ldy, int32_t* acc_out, void* stream);
+int bt_gemv_tiled_i8(const int8_t* Xq, const float* sx, int64_t M, int64_t K,
+                     const uint8_t* tiled, int64_t N, const float* scale, const float* bias,
+                     void* Y, int y_dtype, int64_t ldy, int32_t* acc_out, void* stream);
+
+/*
+ * Prefill-size packed ternary linear on int8 activations (any M >= 1), same
+ * arithmetic as above, contraction on the 5th-generation tensor cores
+ * (tcgen05.mma kind::i8, accumulators in tensor memory).  Reads the tiled layout.
+ * Replaces ternary_linear_packed_forward for large batches
+ * (csrc/kernels/ternary_gemm_production.cu:158-250) and the experimental
+ * mma.sync kernel (csrc/kernels/ternary_gemm_tensor_core.cu:349-657).
+ */
+int bt_gemm_tiled_i8(const int8_t* Xq, const float* sx, int64_t M, int64_t K,
+                     const uint8_t* tiled, int64_t N, const float* scale, const float* bias,
+                     void* Y, int y_dtype, int64_t ldy, int32_t* acc_out, void* stream);
+
+/*
+ * Unpacked-weight linear with floating-point activations, fp32 accumulation:
+ *   Y[b,n] = (sum_k X[b,k] * W[n,k]) * scale[n] + bias[n],   W int8 [N,K]
+ * Replaces `_C.ternary_linear_forward` (csrc/core/dispatch.cpp:52-87;
+ * csrc/kernels/ternary_gemm.cu:41-177).
+ */
+int bt_linear_unpacked(const void* X, int x_dtype, int64_t M, int64_t K,
+                       const int8_t* W, int64_t N, const float* scale, const float* bias,
+                       void* Y, void* stream);
+
+/*
+ * Packed-weight linear with floating-point activations, fp32 accumulation (the
+ * reference's exact float semantics, for callers that need its 1e-4 agreement):
+ *   Y[b,n] = (sum_k X[b,k] * T[n,k]) * scale[n] + bias[n]
+ * Replaces the float arithmetic of `_C.ternary_linear_packed_forward`
+ * (csrc/kernels/ternary_gemm_production.cu:53-250).  Reads the public layout.
+ */
+int bt_linear_packed_float(const void* X, int x_dtype, int64_t M, int64_t K,
+                           const uint8_t* packed_T, int64_t N, const float* scale, const float* bias,
+                           void* Y, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BITTORCH_B200_H */

@@ -1,0 +1,216 @@
+"""GPU tests of the public API (nn modules, ops) — the reference's own test expectations
+re-pointed at this backend.  The integer path is gated against the oracle; the float mode
+against the reference's golden outputs at its own tolerances."""
+
+import numpy as np
+import pytest
+import torch
+import torch.nn as nn
+
+from conftest import golden_cases, load_golden
+
+pytestmark = pytest.mark.gpu
+
+
+def _oracle_int8_forward(oracle, x, codes, scale, bias):
+    q, sx = oracle.act_quant(x)
+    return oracle.epilogue(oracle.gemm_i32(q, codes), sx, scale, bias)
+
+
+def _rel(y, y_ref):
+    return float(np.linalg.norm(y - y_ref) / max(np.linalg.norm(y_ref), 1e-30))
+
+
+def test_config1_ternary_linear_cuda_backend(oracle):
+    """TernaryLinear(512 -> 256, bias, 0.05, backend="cuda") with the golden weights."""
+    import bittorch_b200 as bt
+
+    c = load_golden("c1_linear_512x256")
+    layer = bt.nn.TernaryLinear(512, 256, bias=True, threshold_factor=0.05, backend="cuda").cuda()
+    with torch.no_grad():
+        layer.weight.copy_(torch.from_numpy(c["w"]))
+        layer.bias.copy_(torch.from_numpy(c["bias"]))
+    x = torch.from_numpy(c["x"]).cuda()
+    t, s = layer.get_quantized_weight()
+    assert t.dtype == torch.float32 and np.array_equal(t.cpu().numpy(), c["codes"].astype(np.float32))
+    assert np.array_equal(s.cpu().numpy().view(np.uint32), c["scale"].view(np.uint32))
+    with torch.no_grad():
+        y = layer(x).cpu().numpy()
+    y_ref = _oracle_int8_forward(oracle, c["x"], c["codes"], c["scale"], c["bias"])
+    assert np.array_equal(y.view(np.uint32), y_ref.view(np.uint32))          # integer path: bit exact
+    assert _rel(y, c["y"]) < 2e-2                                             # reported, not gated: int8 activations
+    with torch.no_grad():
+        y_again = layer(x).cpu().numpy()                                      # served from the packed-weight cache
+    assert np.array_equal(y, y_again)
+
+
+def test_float_mode_matches_reference_outputs(monkeypatch):
+    """BITTORCH_B200_ACT=float reproduces the reference's float path at its own 1e-4."""
+    import bittorch_b200 as bt
+
+    monkeypatch.setenv("BITTORCH_B200_ACT", "float")
+    c = load_golden("c1_linear_512x256")
+    layer = bt.nn.TernaryLinear(512, 256, backend="cuda").cuda()
+    with torch.no_grad():
+        layer.weight.copy_(torch.from_numpy(c["w"]))
+        layer.bias.copy_(torch.from_numpy(c["bias"]))
+        y = layer(torch.from_numpy(c["x"]).cuda()).cpu().numpy()
+    assert np.allclose(y, c["y"], rtol=1e-4, atol=1e-4)
+    for name, r in golden_cases(load_golden("ragged_forward")).items():
+        pt = torch.from_numpy(r["packed_T"]).cuda()
+        y = bt.ops.ternary_linear_packed_forward(torch.from_numpy(r["x"]).cuda(), pt, torch.from_numpy(r["scale"]).cuda(),
+                                                 r["x"].shape[1], torch.from_numpy(r["bias"]).cuda())
+        assert np.allclose(y.cpu().numpy(), r["y"], rtol=1e-4, atol=1e-4), name
+        y2 = bt.ops.ternary_linear_forward_cuda(torch.from_numpy(r["x"]).cuda(), torch.from_numpy(r["codes"]).cuda(),
+                                                torch.from_numpy(r["scale"]).cuda(), torch.from_numpy(r["bias"]).cuda())
+        assert np.allclose(y2.cpu().numpy(), r["y"], rtol=1e-4, atol=1e-4), name
+
+
+def test_ragged_shapes_integer_path(oracle):
+    import bittorch_b200 as bt
+
+    for name, r in golden_cases(load_golden("ragged_forward")).items():
+        k = r["x"].shape[1]
+        infer = bt.nn.TernaryLinearInference(k, r["codes"].shape[0], torch.from_numpy(r["packed_T"]).cuda(),
+                                             torch.from_numpy(r["scale"]).cuda(), torch.from_numpy(r["bias"]).cuda())
+        y = infer(torch.from_numpy(r["x"]).cuda()).cpu().numpy()
+        y_ref = _oracle_int8_forward(oracle, r["x"], r["codes"], r["scale"], r["bias"])
+        assert np.array_equal(y.view(np.uint32), y_ref.view(np.uint32)), name
+        y_op = bt.ops.ternary_linear_packed_forward(torch.from_numpy(r["x"]).cuda(), infer.weight_packed, infer.scale, k,
+                                                    infer.bias).cpu().numpy()
+        assert np.array_equal(y_op.view(np.uint32), y_ref.view(np.uint32)), name
+
+
+@pytest.mark.parametrize("m", [1, 4, 16, 40, 300])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_inference_module_batches_and_dtypes(oracle, m, dtype):
+    import bittorch_b200 as bt
+
+    g = torch.Generator().manual_seed(m)
+    k, n = 768, 1152
+    w = torch.randn(n, k, generator=g)
+    b = torch.randn(n, generator=g)
+    infer = bt.nn.create_ternary_linear_inference(k, n, w.cuda(), b.cuda())
+    codes, scale = oracle.ternarize(w.numpy(), 0.05)
+    assert np.array_equal(infer.weight_packed.cpu().numpy(), oracle.pack_transposed(codes))
+    x = torch.randn(2, m, k, generator=g).to(dtype)                # leading batch dims are flattened
+    y = infer(x.cuda())
+    assert y.shape == (2, m, n) and y.dtype == dtype
+    y_ref = _oracle_int8_forward(oracle, x.float().reshape(-1, k).numpy(), codes, scale, b.numpy())
+    assert torch.equal(y.cpu().reshape(-1, n), torch.from_numpy(y_ref).to(dtype))
+
+
+def test_inference_module_state_dict_and_cache_invalidation(oracle, tmp_path):
+    import bittorch_b200 as bt
+
+    g = torch.Generator().manual_seed(1)
+    k, n = 200, 96
+    a = bt.nn.create_ternary_linear_inference(k, n, torch.randn(n, k, generator=g).cuda(), None)
+    b = bt.nn.create_ternary_linear_inference(k, n, torch.randn(n, k, generator=g).cuda(), None)
+    x = torch.randn(5, k, generator=g).cuda()
+    ya, yb = a(x), b(x)
+    assert not torch.equal(ya, yb)
+    assert set(a.state_dict()) == {"weight_packed", "scale"}         # the tiled copy is never serialized
+    path = str(tmp_path / "ckpt.pt")
+    bt.utils.save_ternary_checkpoint(a, path, {"note": "a"})
+    assert bt.utils.load_ternary_checkpoint(path, b) == {"note": "a"}
+    assert torch.equal(b(x), ya)                                        # derived copy rebuilt after load
+    with pytest.raises(RuntimeError, match="CUDA tensor"):
+        a(x.cpu())
+    # a checkpoint packed by the reference loads unchanged
+    c = load_golden("packed_infer_96x200")
+    sd = {"weight_packed": torch.from_numpy(c["packed_T"]), "scale": torch.from_numpy(c["scale"])}
+    b.load_state_dict(sd)
+    y = b(torch.from_numpy(c["x"]).cuda()).cpu().numpy()
+    y_ref = _oracle_int8_forward(oracle, c["x"], c["codes"], c["scale"], None)
+    assert np.array_equal(y.view(np.uint32), y_ref.view(np.uint32))
+
+
+def test_backend_selection_and_errors():
+    import bittorch_b200 as bt
+
+    with pytest.raises(ValueError, match="backend must be"):
+        bt.nn.TernaryLinear(4, 4, backend="triton")
+    layer = bt.nn.TernaryLinear(8, 4, backend="cuda")
+    with pytest.raises(RuntimeError, match="requires input and weights on CUDA"):
+        layer(torch.randn(2, 8))
+    with pytest.raises(RuntimeError, match="requires CUDA"):
+        bt.nn.TernaryLinearCUDA(8, 4)(torch.randn(2, 8))
+    with pytest.warns(DeprecationWarning):
+        assert bt.nn.TernaryLinear(8, 4, use_cuda_kernel=False).backend == "python"
+    debug = bt.nn.TernaryLinear(8, 4, quantize=False).cuda()
+    x = torch.randn(3, 8).cuda()
+    assert torch.allclose(debug(x), torch.nn.functional.linear(x, debug.weight, debug.bias))
+    assert bt.has_cuda_ext() and bt.ops.has_packed_cuda_support()
+    assert torch.equal(bt._C.dummy(x), x)
+
+
+def test_training_step_gradients_match_python_backend(monkeypatch):
+    """Float mode: forward within 1e-4 of the eager backend and identical STE gradients
+    (tests/test_ternary_linear.py:395-412, tests/test_gradient_consistency.py)."""
+    import bittorch_b200 as bt
+
+    monkeypatch.setenv("BITTORCH_B200_ACT", "float")
+    torch.manual_seed(0)
+    ref = bt.nn.TernaryLinear(64, 48, backend="python").cuda()
+    cu = bt.nn.TernaryLinear(64, 48, backend="cuda").cuda()
+    cu.load_state_dict(ref.state_dict())
+    x = torch.randn(10, 64, device="cuda")
+    x1, x2 = x.clone().requires_grad_(True), x.clone().requires_grad_(True)
+    y1, y2 = ref(x1), cu(x2)
+    assert torch.allclose(y1, y2, rtol=1e-4, atol=1e-5)
+    gy = torch.randn_like(y1)
+    y1.backward(gy)
+    y2.backward(gy)
+    assert torch.allclose(x1.grad, x2.grad, rtol=1e-4, atol=1e-5)
+    assert torch.allclose(ref.weight.grad, cu.weight.grad, rtol=1e-4, atol=1e-5)
+    assert torch.allclose(ref.bias.grad, cu.bias.grad, rtol=1e-4, atol=1e-5)
+
+
+def test_training_forward_requantizes_after_an_update():
+    import bittorch_b200 as bt
+
+    torch.manual_seed(1)
+    layer = bt.nn.TernaryLinear(128, 64, backend="cuda").cuda()
+    x = torch.randn(4, 128, device="cuda")
+    opt = torch.optim.SGD(layer.parameters(), lr=0.5)
+    with torch.no_grad():
+        y0 = layer(x)
+    layer(x).square().mean().backward()
+    opt.step()
+    with torch.no_grad():
+        y1 = layer(x)
+    assert not torch.equal(y0, y1)
+    t, s = layer.get_quantized_weight()
+    infer = bt.utils.ternary_linear_to_infer(layer)
+    assert torch.equal(infer(x), y1)
+
+
+def test_convert_linear_layers():
+    import bittorch_b200 as bt
+
+    torch.manual_seed(2)
+    model = nn.Sequential(nn.Linear(64, 32), nn.ReLU(), bt.nn.TernaryLinear(32, 16), nn.Linear(16, 10)).cuda()
+    conv = bt.utils.convert_linear_layers(model, skip_names=["3"])
+    assert isinstance(conv[0], bt.nn.TernaryLinearInference) and isinstance(conv[2], bt.nn.TernaryLinearInference)
+    assert isinstance(conv[3], nn.Linear) and isinstance(model[0], nn.Linear)
+    x = torch.randn(5, 64, device="cuda")
+    assert conv(x).shape == (5, 10)
+    counts = bt.utils.count_ternary_params(conv)
+    assert counts["packed_ternary"] == 64 * 32 + 32 * 16 and counts["fp32"] == 160
+    mem = bt.utils.get_model_memory_bytes(conv)
+    assert mem["packed_ternary"] == 16 * 32 + 8 * 16
+
+
+def test_autocast_forward_backward():
+    import bittorch_b200 as bt
+
+    torch.manual_seed(3)
+    layer = bt.nn.TernaryLinear(64, 32, backend="cuda").cuda()
+    x = torch.randn(8, 64, device="cuda", requires_grad=True)
+    with torch.autocast("cuda", dtype=torch.float16):
+        y = layer(x)
+    assert y.dtype == torch.float16
+    y.float().sum().backward()
+    assert layer.weight.grad is not None and layer.weight.grad.dtype == torch.float32
+    assert torch.isfinite(layer.weight.grad).all() and x.grad is not None
