@@ -10,7 +10,8 @@
 //   warps 2-5    epilogue: tcgen05.ld of the int32 accumulators, un-scale, dequantise, store
 //   warps 6-13   unpack: 2-bit tiles -> signed int8 in the K-major 128-byte-swizzled B tile
 // The unpacked weight of plane i (columns 16i..16i+15 of each 64-column block) is stored as
-// t * 4^i (one mask, one subtract, one xor per four weights); the epilogue shifts it back.
+// t * 4^i for i < 3 (one mask, one subtract, one xor per four weights) and as -t * 64 for
+// i = 3 (one mask-xor); the epilogue shifts (and for plane 3 negates) it back.
 // Accumulators are double-buffered in the 512 TMEM columns so the epilogue of one tile
 // overlaps the main loop of the next.
 // Algorithmic work per call: 2*M*N*K integer ops.
@@ -239,8 +240,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const GemmParams 
                 if (m < p.M && n0 < p.N) {
 #pragma unroll
                     for (int c = 0; c < 32; ++c) {
-                        const int plane = ((c0 + c) % TILE_N) / 16;   // c0 is a multiple of 32, so this folds per c
-                        v[c] >>= 2 * plane;
+                        const int plane = ((c0 + c) % TILE_N) / 16;
+                        v[c] = (plane == 3) ? -(v[c] >> 6) : (v[c] >> (2 * plane));
                     }
                     if (p.acc_out != nullptr) {
 #pragma unroll
@@ -316,9 +317,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const GemmParams 
                     for (int q = 0; q < 4; ++q) {
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
-                            // field (t+1)*4^i  ->  signed byte t*4^i, without borrows between bytes
-                            uint32_t v = (w[q] & (0x03030303u << (2 * i))) | 0x80808080u;
-                            v = (v - (0x01010101u << (2 * i))) ^ 0x80808080u;
+                            // field (t+1)*4^i -> signed byte.  Planes 0-2: t*4^i, subtracting 4^i per
+                            // byte behind a guard bit so no borrow crosses bytes.  Plane 3 owns the top
+                            // two bits, where {0x00,0x40,0x80} ^ 0x40 = {+64, 0, -64} = -t*64 directly;
+                            // the epilogue undoes the sign together with the scale.
+                            uint32_t v;
+                            if (i < 3) {
+                                v = (w[q] & (0x03030303u << (2 * i))) | 0x80808080u;
+                                v = (v - (0x01010101u << (2 * i))) ^ 0x80808080u;
+                            } else {
+                                v = (w[q] & 0xC0C0C0C0u) ^ 0x40404040u;
+                            }
                             const int row = TILE_N * nbl + 16 * i + g + 8 * (q & 1);
                             const int chunk = (2 * ktl + (q >> 1)) ^ (row & 7);
                             *reinterpret_cast<uint32_t*>(bt + (row >> 3) * 1024 + (row & 7) * 128 + chunk * 16 + 4 * t) = v;
