@@ -37,13 +37,14 @@ _SIGNATURES = {
     "bt_quantize_pack": ([_p, _int, _i64, _i64, _i64, _f32, _p, _p, _p, _p, _p], _int),
     "bt_pack_codes": ([_p, _i64, _i64, _p, _p], _int),
     "bt_unpack_codes": ([_p, _i64, _i64, _p, _p], _int),
-    "bt_act_quant_i8": ([_p, _int, _i64, _i64, _i64, _p, _p, _p], _int),
+    "bt_act_quant_i8": ([_p, _int, _i64, _i64, _i64, _p, _p, _p, _p], _int),
     "bt_tiled_bytes": ([_i64, _i64], ctypes.c_size_t),
     "bt_retile_packed": ([_p, _i64, _i64, _p, _p], _int),
     "bt_untile_packed": ([_p, _i64, _i64, _p, _p], _int),
     "bt_gemv_packed_i8": ([_p, _p, _i64, _i64, _p, _i64, _p, _p, _p, _int, _i64, _p, _p], _int),
     "bt_gemv_tiled_i8": ([_p, _p, _i64, _i64, _p, _i64, _p, _p, _p, _int, _i64, _p, _p], _int),
-    "bt_gemm_tiled_i8": ([_p, _p, _i64, _i64, _p, _i64, _p, _p, _p, _int, _i64, _p, _p], _int),
+    "bt_gemv_tiled": ([_p, _int, _i64, _i64, _i64, _p, _i64, _p, _p, _p, _int, _i64, _p, _p, _p, _p], _int),
+    "bt_gemm_tiled_i8": ([_p, _p, _p, _i64, _i64, _p, _i64, _p, _p, _p, _int, _i64, _p, _p], _int),
     "bt_linear_unpacked": ([_p, _int, _i64, _i64, _p, _i64, _p, _p, _p, _p], _int),
     "bt_linear_packed_float": ([_p, _int, _i64, _i64, _p, _i64, _p, _p, _p, _p], _int),
 }
@@ -61,7 +62,11 @@ def _load() -> ctypes.CDLL:
     except OSError as exc:  # pragma: no cover - depends on the machine
         raise ImportError(f"bittorch_b200: cannot load {path}: {exc}") from exc
     for name, (argtypes, restype) in _SIGNATURES.items():
-        fn = getattr(lib, name)   # AttributeError -> a stale library; rebuild
+        try:
+            fn = getattr(lib, name)
+        except AttributeError as exc:
+            raise ImportError(f"bittorch_b200: {path} is stale (no symbol {name}); rebuild it with "
+                              "`python -m bittorch_b200._build`") from exc
         fn.argtypes = argtypes
         fn.restype = restype
     return lib
@@ -180,17 +185,20 @@ def unpack_codes(packed_T: Tensor, in_features: int) -> Tensor:
     return out
 
 
-def act_quant_i8(x2d: Tensor) -> Tuple[Tensor, Tensor]:
-    """Per-row int8 quantization of a [M,K] activation matrix -> (int8 [M,K], float32 [M])."""
+def act_quant_i8(x2d: Tensor, want_sum: bool = False):
+    """Per-row int8 quantization of a [M,K] activation matrix -> (int8 [M,K], float32 [M]),
+    plus the int32 row sums of the codes when ``want_sum`` (an input of ``gemm_tiled_i8``)."""
     _require_cuda(x2d)
     if x2d.stride(1) != 1:
         x2d = x2d.contiguous()
     m, k = x2d.shape
     xq = torch.empty((m, k), dtype=torch.int8, device=x2d.device)
     sx = torch.empty((m,), dtype=torch.float32, device=x2d.device)
+    xsum = torch.empty((m,), dtype=torch.int32, device=x2d.device) if want_sum else None
     with torch.cuda.device(x2d.device):
-        _check(_lib.bt_act_quant_i8(_ptr(x2d), _dtype_code(x2d, "X"), m, k, x2d.stride(0), _ptr(xq), _ptr(sx), _stream(x2d)))
-    return xq, sx
+        _check(_lib.bt_act_quant_i8(_ptr(x2d), _dtype_code(x2d, "X"), m, k, x2d.stride(0), _ptr(xq), _ptr(sx), _ptr(xsum),
+                                    _stream(x2d)))
+    return (xq, sx, xsum) if want_sum else (xq, sx)
 
 
 def tiled_bytes(in_features: int, out_features: int) -> int:
@@ -241,11 +249,43 @@ def gemv_tiled_i8(xq, sx, tiled, in_features, out_features, scale, bias=None, ou
                        want_acc, out)
 
 
+def gemv_tiled(x2d: Tensor, tiled: Tensor, in_features: int, out_features: int, scale: Tensor,
+               bias: Optional[Tensor] = None, out: Optional[Tensor] = None, want_debug: bool = False):
+    """Decode-size linear from floating-point activations in one kernel (fused int8 quantizer).
+
+    ``want_debug`` also returns the int8 activations, their scales and the int32 accumulators.
+    """
+    if x2d.stride(1) != 1:
+        x2d = x2d.contiguous()
+    m = x2d.shape[0]
+    y = torch.empty((m, out_features), dtype=x2d.dtype, device=x2d.device) if out is None else out
+    xq = sx = acc = None
+    if want_debug:
+        xq = torch.empty((m, in_features), dtype=torch.int8, device=x2d.device)
+        sx = torch.empty((m,), dtype=torch.float32, device=x2d.device)
+        acc = torch.empty((m, out_features), dtype=torch.int32, device=x2d.device)
+    with torch.cuda.device(x2d.device):
+        _check(_lib.bt_gemv_tiled(_ptr(x2d), _dtype_code(x2d, "X"), m, in_features, x2d.stride(0), _ptr(tiled), out_features,
+                                  _ptr(scale), _ptr(bias), _ptr(y), _DT[y.dtype], y.stride(0), _ptr(xq), _ptr(sx), _ptr(acc),
+                                  _stream(x2d)))
+    return (y, xq, sx, acc) if want_debug else y
+
+
 def gemm_tiled_i8(xq, sx, tiled, in_features, out_features, scale, bias=None, out_dtype=torch.float32, want_acc=False,
-                  out=None):
-    """Prefill-size integer linear on the tiled layout (tcgen05 tensor cores)."""
-    return _int_linear(_lib.bt_gemm_tiled_i8, xq, sx, tiled, in_features, out_features, scale, bias, out_dtype,
-                       want_acc, out)
+                  out=None, xsum=None):
+    """Prefill-size integer linear on the tiled layout (tcgen05 tensor cores).
+
+    ``xsum``: int32 row sums of ``xq`` as returned by ``act_quant_i8(..., want_sum=True)``;
+    computed here with a torch reduction when not given (tests with hand-made ``xq``)."""
+    if xsum is None:
+        xsum = xq.sum(dim=1, dtype=torch.int32)
+    m = xq.shape[0]
+    y = torch.empty((m, out_features), dtype=out_dtype, device=xq.device) if out is None else out
+    acc = torch.empty((m, out_features), dtype=torch.int32, device=xq.device) if want_acc else None
+    with torch.cuda.device(xq.device):
+        _check(_lib.bt_gemm_tiled_i8(_ptr(xq), _ptr(sx), _ptr(xsum), m, in_features, _ptr(tiled), out_features, _ptr(scale),
+                                     _ptr(bias), _ptr(y), _DT[out_dtype], y.stride(0), _ptr(acc), _stream(xq)))
+    return (y, acc) if want_acc else y
 
 
 def int8_linear_tiled(x2d: Tensor, tiled: Tensor, in_features: int, out_features: int, scale: Tensor,
@@ -255,12 +295,12 @@ def int8_linear_tiled(x2d: Tensor, tiled: Tensor, in_features: int, out_features
     K that is not a multiple of 16 cannot be described to the TMA engine; such ragged
     shapes go through the decode kernel in chunks of 16 rows.
     """
-    xq, sx = act_quant_i8(x2d)
     m = x2d.shape[0]
     if m <= GEMV_MAX_M:
-        return gemv_tiled_i8(xq, sx, tiled, in_features, out_features, scale, bias, x2d.dtype)
+        return gemv_tiled(x2d, tiled, in_features, out_features, scale, bias)
+    xq, sx, xsum = act_quant_i8(x2d, want_sum=True)
     if in_features % 16 == 0:
-        return gemm_tiled_i8(xq, sx, tiled, in_features, out_features, scale, bias, x2d.dtype)
+        return gemm_tiled_i8(xq, sx, tiled, in_features, out_features, scale, bias, x2d.dtype, xsum=xsum)
     y = torch.empty((m, out_features), dtype=x2d.dtype, device=x2d.device)
     for m0 in range(0, m, GEMV_MAX_M):
         m1 = min(m, m0 + GEMV_MAX_M)

@@ -22,8 +22,9 @@ __device__ __forceinline__ int quantize_i8(float v, float inv) {
 template <typename T>
 __global__ void __launch_bounds__(AQ_THREADS)
 act_quant_kernel(const T* __restrict__ X, int64_t K, int64_t ldx, int8_t* __restrict__ Xq,
-                 float* __restrict__ sx, bool vec_in, bool vec_out) {
+                 float* __restrict__ sx, int32_t* __restrict__ xsum, bool vec_in, bool vec_out) {
     __shared__ float s_red[AQ_THREADS / 32];
+    __shared__ int s_sum[AQ_THREADS / 32];
     __shared__ float s_inv;
     pdl_launch_dependents();   // the consumer kernel may start prefetching its weights
     pdl_wait();                // X may be the previous kernel's output
@@ -56,6 +57,7 @@ act_quant_kernel(const T* __restrict__ X, int64_t K, int64_t ldx, int8_t* __rest
     const float inv = s_inv;
 
     int8_t* out = Xq + m * K;
+    int qsum = 0;
     for (int64_t kb = threadIdx.x; kb < KB; kb += AQ_THREADS) {
         float v[4];
         const int64_t k = kb * 4;
@@ -63,7 +65,10 @@ act_quant_kernel(const T* __restrict__ X, int64_t K, int64_t ldx, int8_t* __rest
         load4<T>(row + k, vec_in, valid, v);
         int q[4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) q[i] = quantize_i8(v[i], inv);
+        for (int i = 0; i < 4; ++i) {
+            q[i] = quantize_i8(v[i], inv);
+            if (i < valid) qsum += q[i];
+        }
         if (vec_out && valid == 4) {
             const uint32_t w = (q[0] & 0xff) | ((q[1] & 0xff) << 8) | ((q[2] & 0xff) << 16) | ((q[3] & 0xff) << 24);
             *reinterpret_cast<uint32_t*>(out + k) = w;
@@ -73,14 +78,26 @@ act_quant_kernel(const T* __restrict__ X, int64_t K, int64_t ldx, int8_t* __rest
                 if (i < valid) out[k + i] = static_cast<int8_t>(q[i]);
         }
     }
+    if (xsum != nullptr) {      // row sum of the int8 codes: the tensor-core kernel stores weights as t+1
+        qsum = warp_sum(qsum);
+        if ((threadIdx.x & 31) == 0) s_sum[threadIdx.x >> 5] = qsum;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int t = 0;
+#pragma unroll
+            for (int i = 0; i < AQ_THREADS / 32; ++i) t += s_sum[i];
+            xsum[m] = t;
+        }
+    }
 }
 
 template <typename T>
-static int launch_act_quant(const void* X, int64_t M, int64_t K, int64_t ldx, int8_t* Xq, float* sx, cudaStream_t st) {
+static int launch_act_quant(const void* X, int64_t M, int64_t K, int64_t ldx, int8_t* Xq, float* sx, int32_t* xsum,
+                            cudaStream_t st) {
     const bool vec_in = (K % 4 == 0) && (ldx % 4 == 0) && aligned(X, 4 * sizeof(T));
     const bool vec_out = (K % 4 == 0) && aligned(Xq, 4);
     act_quant_kernel<T><<<static_cast<unsigned>(M), AQ_THREADS, 0, st>>>(static_cast<const T*>(X), K, ldx, Xq, sx,
-                                                                         vec_in, vec_out);
+                                                                         xsum, vec_in, vec_out);
     BT_LAUNCH_OK("act_quant_kernel");
     return BT_OK;
 }
@@ -88,7 +105,7 @@ static int launch_act_quant(const void* X, int64_t M, int64_t K, int64_t ldx, in
 }  // namespace bt
 
 extern "C" int bt_act_quant_i8(const void* X, int x_dtype, int64_t M, int64_t K, int64_t ldx, int8_t* Xq, float* sx,
-                               void* stream) {
+                               int32_t* xsum, void* stream) {
     using namespace bt;
     BT_REQUIRE(X != nullptr && Xq != nullptr && sx != nullptr, "bt_act_quant_i8: NULL pointer");
     BT_REQUIRE(valid_dtype(x_dtype), "bt_act_quant_i8: unknown dtype %d", x_dtype);
@@ -96,7 +113,7 @@ extern "C" int bt_act_quant_i8(const void* X, int x_dtype, int64_t M, int64_t K,
     BT_REQUIRE(ldx >= K, "bt_act_quant_i8: row stride %lld < K %lld", (long long)ldx, (long long)K);
     BT_REQUIRE(M < (int64_t{1} << 31), "bt_act_quant_i8: M too large");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (x_dtype == BT_F32) return launch_act_quant<float>(X, M, K, ldx, Xq, sx, st);
-    if (x_dtype == BT_F16) return launch_act_quant<__half>(X, M, K, ldx, Xq, sx, st);
-    return launch_act_quant<__nv_bfloat16>(X, M, K, ldx, Xq, sx, st);
+    if (x_dtype == BT_F32) return launch_act_quant<float>(X, M, K, ldx, Xq, sx, xsum, st);
+    if (x_dtype == BT_F16) return launch_act_quant<__half>(X, M, K, ldx, Xq, sx, xsum, st);
+    return launch_act_quant<__nv_bfloat16>(X, M, K, ldx, Xq, sx, xsum, st);
 }

@@ -66,6 +66,48 @@ int sm_count();   // SMs of the current device, cached (api.cu)
 __device__ int g_device_status = 0;
 __device__ __forceinline__ void report_wait_timeout() { atomicExch(&g_device_status, BT_ERR_DEVICE_WAIT); }
 
+// Optional timeline stamps for kernel bring-up (compile with -DBT_TRACE): slot `i` of the
+// first CTA's first thread receives the global nanosecond timer.  Compiled out otherwise.
+#ifdef BT_TRACE
+__device__ unsigned long long g_trace[128];
+__device__ __forceinline__ void bt_stamp(int i) {
+    if (blockIdx.x == 0 && blockIdx.y == 0 && (threadIdx.x & 31) == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        if (threadIdx.x == 0) g_trace[i] = t;
+    }
+}
+#define BT_STAMP(i) ::bt::bt_stamp(i)
+// per-warp stamp of CTA 0: slot 32 + warp
+__device__ __forceinline__ void bt_stamp_warp(int base) {
+    if (blockIdx.x == 0 && blockIdx.y == 0 && (threadIdx.x & 31) == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        g_trace[base + (threadIdx.x >> 5)] = t;
+    }
+}
+#define BT_STAMP_WARP(b) ::bt::bt_stamp_warp(b)
+// per-CTA stamps: slot j (0..3) of every CTA (linear block index)
+__device__ unsigned long long g_trace_cta[4096 * 4];
+__device__ unsigned int g_trace_sm[4096];
+__device__ __forceinline__ void bt_stamp_cta(int j) {
+    const unsigned id = blockIdx.x + gridDim.x * blockIdx.y;
+    if (id < 4096 && threadIdx.x == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        g_trace_cta[id * 4 + j] = t;
+        unsigned int smid;
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        g_trace_sm[id] = smid;
+    }
+}
+#define BT_STAMP_CTA(j) ::bt::bt_stamp_cta(j)
+#else
+#define BT_STAMP(i) ((void)0)
+#define BT_STAMP_CTA(j) ((void)0)
+#define BT_STAMP_WARP(b) ((void)0)
+#endif
+
 // ---- device helpers --------------------------------------------------------------
 
 template <typename T> __device__ __forceinline__ float to_float(T v);

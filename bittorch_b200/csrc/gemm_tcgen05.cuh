@@ -8,10 +8,10 @@
 //   warp 1       MMA issuer: 4 x tcgen05.mma.kind::i8 (128x256x32) per K block, commits
 //                free the stage / publish the accumulator
 //   warps 2-5    epilogue: tcgen05.ld of the int32 accumulators, un-scale, dequantise, store
-//   warps 6-13   unpack: 2-bit tiles -> signed int8 in the K-major 128-byte-swizzled B tile
-// The unpacked weight of plane i (columns 16i..16i+15 of each 64-column block) is stored as
-// t * 4^i for i < 3 (one mask, one subtract, one xor per four weights) and as -t * 64 for
-// i = 3 (one mask-xor); the epilogue shifts (and for plane 3 negates) it back.
+//   warps 6-13   unpack: 2-bit tiles -> unsigned bytes t+1 in the K-major 128-byte-swizzled B tile
+// Weights enter the MMA as u8 codes t+1 (one shift and one mask per four weights, four
+// 16-byte shared-memory stores per lane and tile); the epilogue subtracts the row sum of the
+// int8 activations, which the activation quantizer provides.
 // Accumulators are double-buffered in the 512 TMEM columns so the epilogue of one tile
 // overlaps the main loop of the next.
 // Algorithmic work per call: 2*M*N*K integer ops.
@@ -30,7 +30,8 @@ constexpr int GM_BK = 128;                       // bytes = int8 elements per K 
 constexpr int GM_STAGES = 3;
 constexpr int GM_A_BYTES = GM_BM * GM_BK;        // 16 KB
 constexpr int GM_B_BYTES = GM_BN * GM_BK;        // 32 KB
-constexpr int GM_P_BYTES = (GM_BN / TILE_N) * (GM_BK / TILE_K) * TILE_BYTES;   // 8 KB of packed tiles
+constexpr int GM_P_TILES = (GM_BN / TILE_N) * (GM_BK / TILE_K);             // 16 column blocks x 1 k tile
+constexpr int GM_P_BYTES = GM_P_TILES * TILE_BYTES;                          // 8 KB of packed tiles
 constexpr int GM_UNPACK_WARPS = 8;
 constexpr int GM_EPI_WARPS = 4;
 constexpr int GM_THREADS = (2 + GM_EPI_WARPS + GM_UNPACK_WARPS) * 32;          // 448
@@ -40,14 +41,15 @@ constexpr size_t GM_SMEM_BYTES = 1024 /*alignment slack*/ + GM_STAGES * (GM_A_BY
 struct GemmParams {
     const uint8_t* tiled;
     const float* sx;
+    const int32_t* xsum;   // per-row sums of the int8 activations
     const float* scale;
     const float* bias;
     void* Y;
     int32_t* acc_out;
     int64_t ldy;
     int M, K, N;
-    int KT;        // 32-wide k tiles in the tiled layout
-    int NB;        // 64-wide column blocks in the tiled layout
+    int KT;        // 128-wide k tiles in the tiled layout
+    int NB;        // 16-column blocks in the tiled layout
     int y_dtype;
 };
 
@@ -106,8 +108,9 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
     d |= static_cast<uint64_t>(2) << 61;                            // SWIZZLE_128B
     return d;
 }
-// Instruction descriptor: D = s32, A = B = s8, both K-major, M = 128, N = GM_BN.
-constexpr uint32_t GM_IDESC = (2u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(GM_BN >> 3) << 17) |
+// Instruction descriptor: D = s32, A = s8 (activations), B = u8 (weight codes), both K-major,
+// M = 128, N = GM_BN.
+constexpr uint32_t GM_IDESC = (2u << 4) | (1u << 7) | (0u << 10) | (static_cast<uint32_t>(GM_BN >> 3) << 17) |
                               (static_cast<uint32_t>(GM_BM >> 4) << 24);
 
 // Bounded mbarrier wait that also gives up when another role has already failed.
@@ -176,14 +179,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const GemmParams 
                 for (int kb = 0; kb < k_blocks; ++kb, ++it) {
                     const int s = it % GM_STAGES;
                     if (!wait_or_abort(&empty[s], ((it / GM_STAGES) & 1) ^ 1, s_abort)) break;
-                    const int kt0 = kb * (GM_BK / TILE_K);
-                    const int kt_valid = min(GM_BK / TILE_K, p.KT - kt0);
-                    const uint32_t p_bytes = static_cast<uint32_t>(kt_valid) * TILE_BYTES;
-                    mbar_expect_tx(&full_load[s], GM_A_BYTES + static_cast<uint32_t>(nb_valid) * p_bytes);
+                    mbar_expect_tx(&full_load[s], GM_A_BYTES + static_cast<uint32_t>(nb_valid) * TILE_BYTES);
                     tma_load_2d(s_a + s * GM_A_BYTES, &map_x, kb * GM_BK, mt * GM_BM, &full_load[s]);
-                    for (int j = 0; j < nb_valid; ++j)
-                        bulk_g2s(s_p + s * GM_P_BYTES + j * (GM_BK / TILE_K) * TILE_BYTES,
-                                 p.tiled + (static_cast<int64_t>(nb0 + j) * p.KT + kt0) * TILE_BYTES, p_bytes, &full_load[s]);
+                    for (int j = 0; j < nb_valid; ++j)      // one 512-byte tile per 16-column block
+                        bulk_g2s(s_p + s * GM_P_BYTES + j * TILE_BYTES,
+                                 p.tiled + (static_cast<int64_t>(nb0 + j) * p.KT + kb) * TILE_BYTES, TILE_BYTES, &full_load[s]);
                 }
             }
         }
@@ -224,6 +224,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const GemmParams 
             tc_fence_after();
             const int m = mt * GM_BM + lq * 32 + lane;
             const float sxm = (m < p.M) ? p.sx[m] : 0.0f;
+            const int xs = (m < p.M) ? p.xsum[m] : 0;
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(lq * 32) << 16) + a * GM_BN;
 #pragma unroll 1
             for (int c0 = 0; c0 < GM_BN; c0 += 32) {
@@ -239,10 +240,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const GemmParams 
                 const int n0 = nt * GM_BN + c0;
                 if (m < p.M && n0 < p.N) {
 #pragma unroll
-                    for (int c = 0; c < 32; ++c) {
-                        const int plane = ((c0 + c) % TILE_N) / 16;
-                        v[c] = (plane == 3) ? -(v[c] >> 6) : (v[c] >> (2 * plane));
-                    }
+                    for (int c = 0; c < 32; ++c) v[c] -= xs;      // weights were multiplied as t+1
                     if (p.acc_out != nullptr) {
 #pragma unroll
                         for (int c = 0; c < 32; ++c)
@@ -294,7 +292,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const GemmParams 
             }
         }
     } else {
-        // ================= unpack: 2-bit tiles -> signed int8, K-major, 128-byte swizzle =================
+        // ================= unpack: 2-bit tiles -> u8 codes, K-major, 128-byte swizzle =================
         const int utid = threadIdx.x - (2 + GM_EPI_WARPS) * 32;   // 0..255
         const int uwarp = utid >> 5;
         const int g = lane >> 2, t = lane & 3;
@@ -306,31 +304,25 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const GemmParams 
                 if (!wait_or_abort(&full_load[s], (it / GM_STAGES) & 1, s_abort)) { ok = false; break; }
                 const uint8_t* pk = s_p + s * GM_P_BYTES;
                 uint8_t* bt = s_b + s * GM_B_BYTES;
-                // 16 packed tiles (4 column blocks x 4 k tiles) per stage, 2 per warp
+                // 16 packed tiles (16-column blocks) per stage, 2 per warp.  Lane (g,t) holds, for
+                // column g + 8h, the 32 consecutive k = 32t .. 32t+31: two 16-byte chunks per column.
 #pragma unroll
-                for (int u = 0; u < 2; ++u) {
-                    const int tix = uwarp * 2 + u;
-                    const int nbl = tix >> 2, ktl = tix & 3;
+                for (int u = 0; u < GM_P_TILES / GM_UNPACK_WARPS; ++u) {
+                    const int tix = uwarp * (GM_P_TILES / GM_UNPACK_WARPS) + u;
                     const uint4 wv = *reinterpret_cast<const uint4*>(pk + tix * TILE_BYTES + lane * 16);
-                    const uint32_t w[4] = {wv.x, wv.y, wv.z, wv.w};
+                    const uint32_t w[4] = {wv.x, wv.y, wv.z, wv.w};     // word q = h | (h2 << 1)
 #pragma unroll
-                    for (int q = 0; q < 4; ++q) {
+                    for (int h = 0; h < 2; ++h) {
+                        const int row = TILE_N * tix + g + 8 * h;
+                        uint8_t* rowp = bt + (row >> 3) * 1024 + (row & 7) * 128;
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            // field (t+1)*4^i -> signed byte.  Planes 0-2: t*4^i, subtracting 4^i per
-                            // byte behind a guard bit so no borrow crosses bytes.  Plane 3 owns the top
-                            // two bits, where {0x00,0x40,0x80} ^ 0x40 = {+64, 0, -64} = -t*64 directly;
-                            // the epilogue undoes the sign together with the scale.
-                            uint32_t v;
-                            if (i < 3) {
-                                v = (w[q] & (0x03030303u << (2 * i))) | 0x80808080u;
-                                v = (v - (0x01010101u << (2 * i))) ^ 0x80808080u;
-                            } else {
-                                v = (w[q] & 0xC0C0C0C0u) ^ 0x40404040u;
-                            }
-                            const int row = TILE_N * nbl + 16 * i + g + 8 * (q & 1);
-                            const int chunk = (2 * ktl + (q >> 1)) ^ (row & 7);
-                            *reinterpret_cast<uint32_t*>(bt + (row >> 3) * 1024 + (row & 7) * 128 + chunk * 16 + 4 * t) = v;
+                        for (int c = 0; c < 2; ++c) {                   // chunk 2t + c holds planes 2c, 2c+1
+                            uint4 v;
+                            v.x = (w[h] >> (4 * c)) & 0x03030303u;            // plane 2c,   k half 0
+                            v.y = (w[h + 2] >> (4 * c)) & 0x03030303u;        // plane 2c,   k half 1
+                            v.z = (w[h] >> (4 * c + 2)) & 0x03030303u;        // plane 2c+1, k half 0
+                            v.w = (w[h + 2] >> (4 * c + 2)) & 0x03030303u;    // plane 2c+1, k half 1
+                            *reinterpret_cast<uint4*>(rowp + (((2 * t + c) ^ (row & 7)) << 4)) = v;
                         }
                     }
                 }
@@ -372,11 +364,11 @@ static EncodeTiledFn get_encode_tiled() {
 
 }  // namespace bt
 
-extern "C" int bt_gemm_tiled_i8(const int8_t* Xq, const float* sx, int64_t M, int64_t K, const uint8_t* tiled, int64_t N,
-                                const float* scale, const float* bias, void* Y, int y_dtype, int64_t ldy,
-                                int32_t* acc_out, void* stream) {
+extern "C" int bt_gemm_tiled_i8(const int8_t* Xq, const float* sx, const int32_t* xsum, int64_t M, int64_t K,
+                                const uint8_t* tiled, int64_t N, const float* scale, const float* bias, void* Y,
+                                int y_dtype, int64_t ldy, int32_t* acc_out, void* stream) {
     using namespace bt;
-    BT_REQUIRE(Xq && sx && tiled && scale && Y, "bt_gemm_tiled_i8: NULL pointer");
+    BT_REQUIRE(Xq && sx && xsum && tiled && scale && Y, "bt_gemm_tiled_i8: NULL pointer");
     BT_REQUIRE(M > 0 && K > 0 && N > 0, "bt_gemm_tiled_i8: X is empty or weight is empty");
     BT_REQUIRE(valid_dtype(y_dtype), "bt_gemm_tiled_i8: unknown output dtype %d", y_dtype);
     BT_REQUIRE(ldy >= N, "bt_gemm_tiled_i8: output row stride %lld < N %lld", (long long)ldy, (long long)N);
@@ -403,7 +395,7 @@ extern "C" int bt_gemm_tiled_i8(const int8_t* Xq, const float* sx, int64_t M, in
     }
 
     GemmParams p;
-    p.tiled = tiled; p.sx = sx; p.scale = scale; p.bias = bias; p.Y = Y; p.acc_out = acc_out; p.ldy = ldy;
+    p.tiled = tiled; p.sx = sx; p.xsum = xsum; p.scale = scale; p.bias = bias; p.Y = Y; p.acc_out = acc_out; p.ldy = ldy;
     p.M = static_cast<int>(M); p.K = static_cast<int>(K); p.N = static_cast<int>(N);
     p.KT = static_cast<int>(ceil_div<int64_t>(K, TILE_K));
     p.NB = static_cast<int>(ceil_div<int64_t>(N, TILE_N));

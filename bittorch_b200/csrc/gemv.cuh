@@ -1,33 +1,17 @@
-// Decode-size (M <= 16) packed ternary linear on int8 activations.
+// Decode-size (M <= 16) packed ternary linear on int8 activations, compatibility path on the
+// PUBLIC [ceil(K/4), N] buffer (used by the stateless functional API when no tiled copy of
+// the weights exists; modules run gemv_tiled.cuh instead).
 //
-// Two kernels share one skeleton: a thread-block cluster of S CTAs splits K for one
-// block of output columns, every CTA accumulates an int32 partial tile in its own
-// shared memory, and after a cluster barrier each CTA reduces a slice of the columns
-// over distributed shared memory and applies the epilogue.  No global scratch.
-//
-//  * gemv_tiled_kernel  — the bandwidth-bound fast path.  Weights come from the
-//    private tiled layout (512-byte tiles of 64 n x 32 k, see retile.cuh): a producer
-//    lane streams them with 1-D TMA bulk copies into an mbarrier ring, consumer warps
-//    take one 16-byte vector per lane and, by masking the four 2-bit planes in place,
-//    get four ready-made A operands for mma.sync m16n8k32 (u8 x s8 -> s32).  Plane i
-//    holds (t+1)*4^i, so acc_i >> 2i minus the activation row-sum is the exact ternary
-//    dot product.  About one logic op and a quarter MMA per packed byte, independent
-//    of M up to 8 (twice the MMAs up to 16).
-//    Algorithmic HBM bytes per call: ceil(K/4)*N + 4N (+4N bias) + M*K + out.
-//  * gemv_packed_kernel — compatibility path on the public [ceil(K/4), N] buffer
-//    (shared-memory LUT decode + dp4a), used when no tiled copy exists.
+// A thread-block cluster of S CTAs splits K for one block of 128 output columns, every CTA
+// accumulates an int32 partial tile in its own shared memory (shared-memory LUT decode +
+// dp4a), and after a cluster barrier each CTA reduces a slice of the columns over
+// distributed shared memory and applies the epilogue.  No global scratch.
 #pragma once
 
 #include "common.cuh"
-#include "retile.cuh"
 
 namespace bt {
 
-constexpr int GV_CONSUMER_WARPS = 4;
-constexpr int GV_THREADS = (GV_CONSUMER_WARPS + 1) * 32;   // + one producer warp
-constexpr int GV_STAGE_TILES = 8;                          // 4 KB per stage
-constexpr int GV_STAGE_BYTES = GV_STAGE_TILES * TILE_BYTES;
-constexpr int GV_STAGES = 8;                               // 32 KB ring per CTA
 constexpr int GV_X_PAD = 16;                               // row padding of the activation slice (bank spread)
 
 struct GemvParams {
@@ -103,134 +87,7 @@ __device__ __forceinline__ void cluster_reduce_store(const GemvParams& p, const 
         const float y = dequant(acc, p.sx[m], p.scale[n], p.bias ? p.bias[n] : 0.0f, p.bias != nullptr);
         store_out_dt(p.Y, p.y_dtype, static_cast<int64_t>(m) * p.ldy + n, y);
     }
-}
-
-// ------------------------------------------------------------------------------------
-// Fast path: tiled layout, TMA ring, mma.sync.
-// grid = (S, ceil(N/64)), cluster = (S,1,1), block = 160 threads, dynamic smem.
-// ------------------------------------------------------------------------------------
-template <int MT>   // MT n8-blocks of activations rows: M <= 8*MT
-__global__ void __launch_bounds__(GV_THREADS)
-gemv_tiled_kernel(const GemvParams p) {
-    constexpr int M_PAD = 8 * MT;
-    extern __shared__ __align__(128) uint8_t smem[];
-    const int xstride = p.slice_max * TILE_K + GV_X_PAD;
-    uint8_t* s_ring = smem;
-    int8_t* s_x = reinterpret_cast<int8_t*>(smem + GV_STAGES * GV_STAGE_BYTES);
-    int* s_acc = reinterpret_cast<int*>(s_x + ((M_PAD * xstride + 15) / 16) * 16);
-    int* s_rowsum = s_acc + TILE_N * M_PAD;
-    uint64_t* s_full = reinterpret_cast<uint64_t*>(s_rowsum + M_PAD);   // offset is a multiple of 8 bytes
-    uint64_t* s_empty = s_full + GV_STAGES;
-    __shared__ int s_abort;
-
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const uint32_t S = cluster_nctarank(), rank = cluster_ctarank();
-    const int nb = blockIdx.y;
-    const int kt0 = static_cast<int>((static_cast<int64_t>(rank) * p.KT) / S);
-    const int kt1 = static_cast<int>((static_cast<int64_t>(rank + 1) * p.KT) / S);
-    const int nt = kt1 - kt0;
-    const int n_iters = (nt + GV_STAGE_TILES - 1) / GV_STAGE_TILES;
-    const uint8_t* src = p.W + (static_cast<int64_t>(nb) * p.KT + kt0) * TILE_BYTES;
-
-    if (tid == 0) {
-        for (int s = 0; s < GV_STAGES; ++s) {
-            mbar_init(&s_full[s], 1);
-            mbar_init(&s_empty[s], GV_CONSUMER_WARPS);
-        }
-        s_abort = 0;
-        mbar_fence_init();
-    }
-    for (int i = tid; i < TILE_N * M_PAD; i += GV_THREADS) s_acc[i] = 0;
-    __syncthreads();
-    pdl_launch_dependents();
-
-    if (warp == GV_CONSUMER_WARPS) {
-        // ---- producer: one lane streams this CTA's contiguous run of tiles -------------
-        // The weights are never written by a preceding kernel, so the stream starts
-        // before the dependency wait below.
-        if (lane == 0) {
-            for (int it = 0; it < n_iters; ++it) {
-                const int s = it % GV_STAGES;
-                if (it >= GV_STAGES) {
-                    if (!mbar_wait_bounded(&s_empty[s], ((it / GV_STAGES) - 1) & 1)) {
-                        report_wait_timeout();
-                        atomicExch(&s_abort, 1);
-                        break;
-                    }
-                }
-                const uint32_t bytes = static_cast<uint32_t>(min(GV_STAGE_TILES, nt - it * GV_STAGE_TILES)) * TILE_BYTES;
-                mbar_expect_tx(&s_full[s], bytes);
-                bulk_g2s(s_ring + s * GV_STAGE_BYTES, src + static_cast<int64_t>(it) * GV_STAGE_BYTES, bytes, &s_full[s]);
-            }
-        }
-    } else {
-        // ---- consumers ---------------------------------------------------------------------
-        pdl_wait();   // activations come from the preceding kernel
-        stage_activations<M_PAD>(p, kt0 * TILE_K, nt * TILE_K, xstride, s_x, s_rowsum, tid, GV_CONSUMER_WARPS * 32, 1);
-
-        int acc[MT][4][4];
-#pragma unroll
-        for (int a = 0; a < MT; ++a)
-#pragma unroll
-            for (int b = 0; b < 4; ++b)
-#pragma unroll
-                for (int c = 0; c < 4; ++c) acc[a][b][c] = 0;
-        const int g = lane >> 2, t = lane & 3;
-
-        for (int it = 0; it < n_iters; ++it) {
-            const int s = it % GV_STAGES;
-            if (!mbar_wait_bounded(&s_full[s], (it / GV_STAGES) & 1)) {
-                report_wait_timeout();
-                atomicExch(&s_abort, 1);
-                break;
-            }
-#pragma unroll
-            for (int u = 0; u < GV_STAGE_TILES / GV_CONSUMER_WARPS; ++u) {
-                const int jl = warp + u * GV_CONSUMER_WARPS;
-                const int j = it * GV_STAGE_TILES + jl;
-                if (j < nt) {
-                    const uint4 wv = *reinterpret_cast<const uint4*>(s_ring + s * GV_STAGE_BYTES + jl * TILE_BYTES + lane * 16);
-#pragma unroll
-                    for (int mt = 0; mt < MT; ++mt) {
-                        const int8_t* xr = s_x + (g + 8 * mt) * xstride + j * TILE_K + 4 * t;
-                        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(xr);
-                        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(xr + 16);
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const uint32_t mask = 0x03030303u << (2 * i);
-                            const uint32_t a[4] = {wv.x & mask, wv.y & mask, wv.z & mask, wv.w & mask};
-                            mma_u8s8_16x8x32(acc[mt][i], a, b0, b1);
-                        }
-                    }
-                }
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&s_empty[s]);
-        }
-        // plane i carries a factor 4^i; D fragment: rows g, g+8 (columns n), cols 2t, 2t+1 (rows m)
-#pragma unroll
-        for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-            for (int i = 0; i < 4; ++i)
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    const int nl = 16 * i + g + 8 * (c >> 1);
-                    const int m = 8 * mt + 2 * t + (c & 1);
-                    atomicAdd(&s_acc[nl * M_PAD + m], acc[mt][i][c] >> (2 * i));
-                }
-    }
-    __syncthreads();
-    if (s_abort && tid == 0) {
-        // Give copies that may still be in flight a bounded chance to land before the
-        // shared memory is released.
-        for (int s = 0; s < GV_STAGES && s < n_iters; ++s) {
-            const int last_it = ((n_iters - 1 - s) / GV_STAGES) * GV_STAGES + s;
-            mbar_wait_bounded(&s_full[s], (last_it / GV_STAGES) & 1, 1u << 16);
-        }
-    }
-    cluster_sync_all();
-    if (!s_abort) cluster_reduce_store<M_PAD>(p, s_acc, s_rowsum, TILE_N, nb * TILE_N, rank, S, true, tid, GV_THREADS);
-    cluster_sync_all();   // nobody leaves while a peer may still read its shared memory
+    BT_STAMP(10);
 }
 
 // ------------------------------------------------------------------------------------
@@ -318,6 +175,11 @@ gemv_packed_kernel(const GemvParams p) {
 // ---- host side -------------------------------------------------------------------------
 
 static int pick_split(int col_blocks, int k_units, int min_units_per_cta) {
+    // Testing / tuning override: BITTORCH_B200_GEMV_SPLIT = 1, 2, 4 or 8.
+    if (const char* e = std::getenv("BITTORCH_B200_GEMV_SPLIT")) {
+        const int v = std::atoi(e);
+        if (v == 1 || v == 2 || v == 4 || v == 8) return (k_units >= v) ? v : 1;
+    }
     int S = 1;
     const int want = 3 * sm_count();
     while (S < 8 && col_blocks * S < want && k_units / (2 * S) >= min_units_per_cta) S *= 2;
@@ -372,31 +234,6 @@ static GemvParams make_params(const int8_t* Xq, const float* sx, int64_t M, int6
 }
 
 }  // namespace bt
-
-extern "C" int bt_gemv_tiled_i8(const int8_t* Xq, const float* sx, int64_t M, int64_t K, const uint8_t* tiled,
-                                int64_t N, const float* scale, const float* bias, void* Y, int y_dtype, int64_t ldy,
-                                int32_t* acc_out, void* stream) {
-    using namespace bt;
-    int rc = check_gemv_args("bt_gemv_tiled_i8", Xq, sx, M, K, tiled, N, scale, Y, y_dtype, ldy);
-    if (rc != BT_OK) return rc;
-    BT_UNSUPPORTED_IF(M > BT_GEMV_MAX_M, "bt_gemv_tiled_i8: M=%lld exceeds %d", (long long)M, BT_GEMV_MAX_M);
-    BT_REQUIRE(aligned(tiled, 16), "bt_gemv_tiled_i8: tiled weights must be 16-byte aligned");
-    GemvParams p = make_params(Xq, sx, M, K, tiled, N, scale, bias, Y, y_dtype, ldy, acc_out);
-    p.KT = static_cast<int>(ceil_div<int64_t>(K, TILE_K));
-    const int NB = static_cast<int>(ceil_div<int64_t>(N, TILE_N));
-    const int m_pad = (M <= 8) ? 8 : 16;
-    int S = pick_split(NB, p.KT, 4);
-    // keep the activation slice (m_pad rows) within 64 KB of shared memory where a split allows it
-    while (S < 8 && static_cast<int64_t>(m_pad) * ceil_div(p.KT, S) * TILE_K > 64 * 1024 && p.KT / (2 * S) >= 1) S *= 2;
-    p.slice_max = ceil_div(p.KT, S);
-    const int xstride = p.slice_max * TILE_K + GV_X_PAD;
-    const size_t smem = static_cast<size_t>(GV_STAGES) * GV_STAGE_BYTES + ((static_cast<size_t>(m_pad) * xstride + 15) / 16) * 16 +
-                        sizeof(int) * (TILE_N * m_pad + m_pad) + sizeof(uint64_t) * 2 * GV_STAGES;
-    dim3 grid(S, NB), block(GV_THREADS);
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (m_pad == 8) return launch_cluster(gemv_tiled_kernel<1>, "gemv_tiled_kernel<1>", grid, block, smem, S, st, p);
-    return launch_cluster(gemv_tiled_kernel<2>, "gemv_tiled_kernel<2>", grid, block, smem, S, st, p);
-}
 
 extern "C" int bt_gemv_packed_i8(const int8_t* Xq, const float* sx, int64_t M, int64_t K, const uint8_t* packed_T,
                                  int64_t N, const float* scale, const float* bias, void* Y, int y_dtype, int64_t ldy,

@@ -1,0 +1,514 @@
+// Decode-size packed ternary linear on the tiled layout: the HBM-bound fast path.
+//
+// One CTA per SM (grid = min(#SMs, column blocks)), no clusters, no global scratch.  Each
+// CTA owns a contiguous run of 16-column blocks, i.e. one contiguous byte range of the
+// tiled buffer, which a producer lane streams with 1-D TMA bulk copies into an mbarrier
+// ring (8 KB stages, up to 64 KB) — starting BEFORE the programmatic-dependent-launch wait,
+// because weights never depend on the preceding kernel, so with back-to-back layers the
+// weight stream of layer i+1 overlaps the tail of layer i.
+//
+// After the wait the CTA (16 consumer warps) quantizes the activation rows itself (FUSED:
+// per-row absmax over all of K, reciprocal scale, roundf, clamp — bit-identical to
+// bt_act_quant_i8) or copies pre-quantized int8 rows, into shared memory.  Then warp w
+// takes tile 16*stage + w: one 16-byte vector per lane, the four 2-bit planes masked in
+// place (bytes (t+1)*4^i for planes 0..2, -t*64 for plane 3), each masked word a dp4a against
+// the matching activation word.  Per tile and activation row: 16 logic ops shared by all rows + 16 dp4a.  When a
+// warp leaves a column block it folds its planes (>> 2i), sums the four k-lanes with
+// shuffles and parks 16 sums per row in its own slot of shared memory; at the end the CTA
+// adds the 16 warps' slots, subtracts the row sum of the activations that met planes 0..2
+// (whose codes are stored as t+1) and applies (float(acc) * sx) * scale + bias.
+//
+// Algorithmic HBM bytes per call: ceil(K/4)*N + 4N (+4N bias) + x + y.
+#pragma once
+
+#include "act_quant.cuh"
+#include "common.cuh"
+#include "retile.cuh"
+
+namespace bt {
+
+constexpr int GT_CONSUMER_WARPS = 16;
+constexpr int GT_NCONS = GT_CONSUMER_WARPS * 32;
+constexpr int GT_THREADS = GT_NCONS + 32;              // + one producer warp
+constexpr int GT_STAGE_TILES = 16;                     // one tile per consumer warp
+constexpr int GT_STAGE_BYTES = GT_STAGE_TILES * TILE_BYTES;   // 8 KB
+constexpr int GT_MAX_STAGES = 8;                       // up to 64 KB of weights in flight per CTA
+constexpr int GT_MAX_ROWS = 8;                         // activation rows per launch (accumulators live in registers)
+constexpr int GT_X_PAD = 16;                           // bytes of padding per activation row in shared memory
+constexpr int GT_SLOT_BUDGET = 32;                     // column blocks per CTA x padded rows, bounds the partial-sum slots
+
+struct GemvTiledParams {
+    const void* X;         // FUSED: floating-point activations [M,K], row stride ldx
+    const int8_t* Xq;      // else: int8 activations [M,K] contiguous
+    const float* sx;       //       and their per-row scales
+    const uint8_t* W;      // tiled weights
+    const float* scale;
+    const float* bias;
+    void* Y;
+    int8_t* xq_out;        // FUSED, optional: the int8 activations the kernel computed
+    float* sx_out;         // FUSED, optional: their scales
+    int32_t* acc_out;      // optional: int32 accumulators [M,N]
+    int64_t ldx, ldy;
+    int M, K, N;
+    int KT;                // 128-wide k tiles per column block
+    int NB;                // 16-column blocks
+    int nbl_max;           // column blocks per CTA (upper bound)
+    int stages;            // ring depth
+    int x_dtype, y_dtype;
+    int x_vec;             // activation rows can be read with vector loads
+};
+
+// Loads 4 consecutive activations of runtime dtype as float.
+__device__ __forceinline__ void load_x4(const void* X, int dtype, int64_t idx, bool vec, int valid, float (&out)[4]) {
+    if (dtype == BT_BF16) load4<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(X) + idx, vec, valid, out);
+    else if (dtype == BT_F16) load4<__half>(static_cast<const __half*>(X) + idx, vec, valid, out);
+    else load4<float>(static_cast<const float*>(X) + idx, vec, valid, out);
+}
+
+// Two CTAs per SM (<= 56 registers) for the small row counts, so that the next layer's CTAs
+// can move in and prefetch their weights while this layer finishes.
+template <int MR, bool FUSED>   // MR = activation rows padded to a power of two: 1, 2, 4 or 8
+__global__ void __launch_bounds__(GT_THREADS, (MR <= 2) ? 2 : 1)
+gemv_tiled_kernel(const GemvTiledParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int k_pad = p.KT * TILE_K;
+    const int xstride = k_pad + GT_X_PAD;
+    uint8_t* s_ring = smem;
+    int8_t* s_x = reinterpret_cast<int8_t*>(smem + p.stages * GT_STAGE_BYTES);             // [MR][xstride]
+    int* s_part = reinterpret_cast<int*>(s_x + MR * xstride);                                // [16 warps][nbl_max][16][MR]
+    int* s_rowsum = s_part + GT_CONSUMER_WARPS * p.nbl_max * TILE_N * MR;                    // [MR]
+    int* s_wsum = s_rowsum + MR;                                                             // [16 warps][MR]
+    float* s_wmax = reinterpret_cast<float*>(s_wsum + GT_CONSUMER_WARPS * MR);               // [16 warps][MR]
+    float* s_sx = s_wmax + GT_CONSUMER_WARPS * MR;                                           // [MR]
+    float* s_scale = s_sx + MR;                                                              // [nbl_max*16] weight scales
+    float* s_bias = s_scale + p.nbl_max * TILE_N;                                            // [nbl_max*16]
+    uint64_t* s_full = reinterpret_cast<uint64_t*>((reinterpret_cast<uintptr_t>(s_bias + p.nbl_max * TILE_N) + 7) & ~uintptr_t(7));
+    uint64_t* s_empty = s_full + p.stages;
+    __shared__ int s_abort;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int stages = p.stages;
+    // this CTA's run of column blocks and tiles
+    const int nb0 = static_cast<int>((static_cast<int64_t>(blockIdx.x) * p.NB) / gridDim.x);
+    const int nb1 = static_cast<int>((static_cast<int64_t>(blockIdx.x + 1) * p.NB) / gridDim.x);
+    const int nbl = nb1 - nb0;
+    const int nt = nbl * p.KT;
+    const int n_iters = (nt + GT_STAGE_TILES - 1) / GT_STAGE_TILES;
+    const uint8_t* src = p.W + static_cast<int64_t>(nb0) * p.KT * TILE_BYTES;
+    BT_STAMP(0);
+    BT_STAMP_CTA(0);
+
+    if (tid == 0) {
+        for (int s = 0; s < stages; ++s) {
+            mbar_init(&s_full[s], 1);
+            mbar_init(&s_empty[s], GT_CONSUMER_WARPS);
+        }
+        s_abort = 0;
+        mbar_fence_init();
+    }
+    for (int i = tid; i < GT_CONSUMER_WARPS * p.nbl_max * TILE_N * MR + MR + 2 * GT_CONSUMER_WARPS * MR; i += GT_THREADS)
+        s_part[i] = 0;                                  // s_part, s_rowsum, s_wsum, s_wmax (0.0f)
+    for (int c = tid; c < nbl * TILE_N; c += GT_THREADS) {   // epilogue constants: never written by a preceding kernel
+        const int n = nb0 * TILE_N + c;
+        s_scale[c] = (n < p.N) ? p.scale[n] : 0.0f;
+        s_bias[c] = (p.bias != nullptr && n < p.N) ? p.bias[n] : 0.0f;
+    }
+    __syncthreads();
+    pdl_launch_dependents();
+    BT_STAMP(1);
+
+    if (warp == GT_CONSUMER_WARPS) {
+        // ---- producer: one lane streams this CTA's contiguous byte range --------------------
+        if (lane == 0) {
+            int s = 0;
+            uint32_t wrap_parity = 1;                        // parity of the "previous use" phase of the slot
+            for (int it = 0; it < n_iters; ++it) {
+                if (it >= stages) {
+                    if (!mbar_wait_bounded(&s_empty[s], wrap_parity)) {
+                        report_wait_timeout();
+                        atomicExch(&s_abort, 1);
+                        break;
+                    }
+                }
+                const uint32_t bytes = static_cast<uint32_t>(min(GT_STAGE_TILES, nt - it * GT_STAGE_TILES)) * TILE_BYTES;
+                mbar_expect_tx(&s_full[s], bytes);
+                bulk_g2s(s_ring + s * GT_STAGE_BYTES, src + static_cast<int64_t>(it) * GT_STAGE_BYTES, bytes, &s_full[s]);
+                if (++s == stages) { s = 0; wrap_parity ^= 1; }
+            }
+        }
+    } else {
+        // ---- consumers --------------------------------------------------------------------------
+        pdl_wait();   // activations come from the preceding kernel
+        BT_STAMP(3);
+        BT_STAMP_CTA(1);
+        if (FUSED) {
+            // thread -> (row, 4-element vector): the 512 consumer threads are split evenly over
+            // the next power of two >= M rows; thread j of a row takes vectors j, j+tpr, ...
+            const int tpr = GT_NCONS / MR;                  // threads per row: 512 .. 64 (whole warps)
+            const int m = tid / tpr, j = tid % tpr;
+            const int nvec = (p.K + 3) / 4;
+            const bool row_ok = m < p.M;
+            const int64_t row_off = static_cast<int64_t>(m) * p.ldx;
+            // a row that fits four vectors per thread stays in registers between the two passes
+            const bool single = nvec <= 4 * tpr;
+            float x[4][4];
+            float mx = 0.0f;
+            if (row_ok) {
+                for (int v0 = j; v0 < nvec; v0 += 4 * tpr) {
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {           // four independent loads in flight
+                        const int v = v0 + u * tpr;
+                        const int valid = (v < nvec) ? min(4, p.K - 4 * v) : 0;
+                        if (valid > 0) load_x4(p.X, p.x_dtype, row_off + 4 * v, p.x_vec, valid, x[u]);
+                        else x[u][0] = x[u][1] = x[u][2] = x[u][3] = 0.0f;
+                    }
+#pragma unroll
+                    for (int u = 0; u < 4; ++u)
+                        mx = fmaxf(fmaxf(fmaxf(mx, fabsf(x[u][0])), fmaxf(fabsf(x[u][1]), fabsf(x[u][2]))), fabsf(x[u][3]));
+                }
+            }
+            BT_STAMP(2);
+            BT_STAMP_WARP(32);
+            mx = warp_max(mx);                              // a warp never straddles two rows (tpr >= 64)
+            if (lane == 0 && row_ok) s_wmax[warp * MR + m] = mx;
+            asm volatile("bar.sync 1, %0;" ::"r"(GT_NCONS) : "memory");
+            BT_STAMP(4);
+            float amax = 0.0f;
+#pragma unroll
+            for (int w = 0; w < GT_CONSUMER_WARPS; ++w) amax = fmaxf(amax, s_wmax[w * MR + (row_ok ? m : 0)]);
+            // csrc/kernels/ternary_gemm_tensor_core.cu:438-440 (scale rule) and :456 (reciprocal)
+            const float sxm = (amax > 1e-6f) ? __fdiv_rn(amax, 127.0f) : 1.0f;
+            const float inv = __fdiv_rn(1.0f, sxm);
+            if (row_ok && j == 0) {
+                s_sx[m] = sxm;
+                if (p.sx_out != nullptr && blockIdx.x == 0) p.sx_out[m] = sxm;
+            }
+            // zero what the quantizer will not write: padding rows and the tail past K
+            {
+                const int vecs = xstride / 16;
+                const int first_tail = p.K / 16;            // first 16-byte vector that is not entirely real data
+                for (int mm = 0; mm < MR; ++mm)
+                    for (int vv = (mm >= p.M ? 0 : first_tail) + tid; vv < vecs; vv += GT_NCONS)
+                        *reinterpret_cast<uint4*>(s_x + mm * xstride + vv * 16) = make_uint4(0, 0, 0, 0);
+            }
+            if (p.K % 16 != 0) asm volatile("bar.sync 1, %0;" ::"r"(GT_NCONS) : "memory");   // tail bytes are rewritten below
+            BT_STAMP(5);
+            int qsum = 0;
+            if (row_ok) {
+                const bool emit = (p.xq_out != nullptr) && blockIdx.x == 0;
+                for (int v0 = j; v0 < nvec; v0 += 4 * tpr) {
+                    if (!single) {
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            const int v = v0 + u * tpr;
+                            const int valid = (v < nvec) ? min(4, p.K - 4 * v) : 0;
+                            if (valid > 0) load_x4(p.X, p.x_dtype, row_off + 4 * v, p.x_vec, valid, x[u]);
+                        }
+                    }
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const int v = v0 + u * tpr;
+                        const int valid = (v < nvec) ? min(4, p.K - 4 * v) : 0;
+                        if (valid <= 0) continue;
+                        uint32_t w = 0;
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            if (i < valid) w |= static_cast<uint32_t>(quantize_i8(x[u][i], inv) & 0xff) << (8 * i);
+                        if (((v >> 1) & 3) != 3) qsum = __dp4a(static_cast<int>(w), 0x01010101, qsum);   // planes 0..2 only
+                        if (valid == 4) {
+                            *reinterpret_cast<uint32_t*>(s_x + m * xstride + 4 * v) = w;
+                        } else {
+                            for (int i = 0; i < valid; ++i) s_x[m * xstride + 4 * v + i] = static_cast<int8_t>(w >> (8 * i));
+                        }
+                        if (emit)
+                            for (int i = 0; i < valid; ++i)
+                                p.xq_out[static_cast<int64_t>(m) * p.K + 4 * v + i] = static_cast<int8_t>(w >> (8 * i));
+                    }
+                }
+            }
+            BT_STAMP(14);
+            qsum = warp_sum(qsum);
+            if (lane == 0 && row_ok) s_wsum[warp * MR + m] = qsum;
+        } else {
+            // pre-quantized activations: copy the rows (padding rows and the tail are zero)
+            const int vecs = xstride / 16;
+            if (p.x_vec) {                                   // K % 16 == 0 and Xq 16-byte aligned
+                for (int mm = 0; mm < MR; ++mm)
+                    for (int vv = tid; vv < vecs; vv += GT_NCONS) {
+                        uint4 val = make_uint4(0, 0, 0, 0);
+                        if (mm < p.M && vv * 16 < p.K)
+                            val = *reinterpret_cast<const uint4*>(p.Xq + static_cast<int64_t>(mm) * p.K + vv * 16);
+                        *reinterpret_cast<uint4*>(s_x + mm * xstride + vv * 16) = val;
+                    }
+            } else {
+                for (int mm = 0; mm < MR; ++mm)
+                    for (int b = tid; b < xstride; b += GT_NCONS)
+                        s_x[mm * xstride + b] = (mm < p.M && b < p.K) ? p.Xq[static_cast<int64_t>(mm) * p.K + b] : int8_t(0);
+            }
+            if (tid < MR) s_sx[tid] = (tid < p.M) ? p.sx[tid] : 0.0f;
+            asm volatile("bar.sync 1, %0;" ::"r"(GT_NCONS) : "memory");
+            // row sums: warp w sums its share of every row
+            for (int mm = 0; mm < MR; ++mm) {
+                int sum = 0;
+                for (int w = tid; w < k_pad / 4; w += GT_NCONS)
+                    if (((w >> 1) & 3) != 3)                 // planes 0..2 only (plane 3 is stored sign-exact)
+                        sum = __dp4a(*reinterpret_cast<const int*>(s_x + mm * xstride + w * 4), 0x01010101, sum);
+                sum = warp_sum(sum);
+                if (lane == 0) s_wsum[warp * MR + mm] = sum;
+            }
+        }
+        asm volatile("bar.sync 1, %0;" ::"r"(GT_NCONS) : "memory");      // int8 rows complete in shared memory
+        if (tid < MR) {
+            int sum = 0;
+#pragma unroll
+            for (int w = 0; w < GT_CONSUMER_WARPS; ++w) sum += s_wsum[w * MR + tid];
+            s_rowsum[tid] = sum;                             // read after the final CTA barrier
+        }
+        BT_STAMP(6);
+        BT_STAMP_CTA(2);
+
+        // Lane (g,t), per tile: plane i / word q = four consecutive k of column g + 8(q&1),
+        // k = 32t + 8i + 4(q>>1).  acc[m][i][h]: plane i of column g + 8h.
+        int acc[MR][4][2];
+#pragma unroll
+        for (int a = 0; a < MR; ++a)
+#pragma unroll
+            for (int b = 0; b < 4; ++b) acc[a][b][0] = acc[a][b][1] = 0;
+        const int g = lane >> 2, t = lane & 3;
+        int cur_nb = -1;                                    // column block (local) the accumulators belong to
+
+        // folds the planes, sums the four k-lanes and parks the 16 column sums of each row
+        auto flush = [&](int nb_local) {
+#pragma unroll
+            for (int m = 0; m < MR; ++m) {
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    int v = acc[m][0][h] + (acc[m][1][h] >> 2) + (acc[m][2][h] >> 4) - (acc[m][3][h] >> 6);
+                    v += __shfl_xor_sync(0xffffffffu, v, 1);
+                    v += __shfl_xor_sync(0xffffffffu, v, 2);
+                    if (t == 0) s_part[((warp * p.nbl_max + nb_local) * TILE_N + g + 8 * h) * MR + m] = v;
+                    acc[m][0][h] = acc[m][1][h] = acc[m][2][h] = acc[m][3][h] = 0;
+                }
+            }
+        };
+
+        // no divisions in the loop: slot / parity and (column block, k tile) advance incrementally
+        int s = 0;
+        uint32_t parity = 0;
+        int nb_local = 0, kt = warp;                        // tile `warp` of the chunk
+        while (kt >= p.KT) { kt -= p.KT; ++nb_local; }
+        for (int it = 0; it < n_iters; ++it) {
+            if (!mbar_wait_bounded(&s_full[s], parity)) {
+                report_wait_timeout();
+                atomicExch(&s_abort, 1);
+                break;
+            }
+            if (it == 0) BT_STAMP(10);
+            if (it == 1) BT_STAMP(11);
+            if (it == 2) BT_STAMP(15);
+            if (it == 1) BT_STAMP_WARP(64);
+            if (nb_local < nbl) {                            // this warp has a tile in this stage
+                if (nb_local != cur_nb) {
+                    if (cur_nb >= 0) flush(cur_nb);
+                    cur_nb = nb_local;
+                }
+                const uint4 wv = *reinterpret_cast<const uint4*>(s_ring + s * GT_STAGE_BYTES + warp * TILE_BYTES + lane * 16);
+                // planes 0..2: bytes (t+1)*4^i, at most 32, valid as signed; plane 3 owns the top
+                // two bits, where {0x00,0x40,0x80} ^ 0x40 = {+64, 0, -64} = -t*64 as signed bytes
+                int wm[4][4];
+#pragma unroll
+                for (int i = 0; i < 3; ++i) {
+                    const uint32_t mask = 0x03030303u << (2 * i);
+                    wm[i][0] = wv.x & mask; wm[i][1] = wv.y & mask; wm[i][2] = wv.z & mask; wm[i][3] = wv.w & mask;
+                }
+                wm[3][0] = (wv.x & 0xC0C0C0C0u) ^ 0x40404040u; wm[3][1] = (wv.y & 0xC0C0C0C0u) ^ 0x40404040u;
+                wm[3][2] = (wv.z & 0xC0C0C0C0u) ^ 0x40404040u; wm[3][3] = (wv.w & 0xC0C0C0C0u) ^ 0x40404040u;
+#pragma unroll
+                for (int m = 0; m < MR; ++m) {
+                    // 32 consecutive activations: word 2i + (q>>1)
+                    const int8_t* xp = s_x + m * xstride + kt * TILE_K + 32 * t;
+                    const int4 xa = *reinterpret_cast<const int4*>(xp);
+                    const int4 xb = *reinterpret_cast<const int4*>(xp + 16);
+                    const int xw[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        acc[m][i][0] = __dp4a(wm[i][0], xw[2 * i], acc[m][i][0]);
+                        acc[m][i][1] = __dp4a(wm[i][1], xw[2 * i], acc[m][i][1]);
+                        acc[m][i][0] = __dp4a(wm[i][2], xw[2 * i + 1], acc[m][i][0]);
+                        acc[m][i][1] = __dp4a(wm[i][3], xw[2 * i + 1], acc[m][i][1]);
+                    }
+                }
+            }
+            if (it == 1) BT_STAMP_WARP(80);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&s_empty[s]);
+            if (it == 1) BT_STAMP_WARP(96);
+            if (++s == stages) { s = 0; parity ^= 1; }
+            kt += GT_STAGE_TILES;
+            while (kt >= p.KT) { kt -= p.KT; ++nb_local; }
+        }
+        BT_STAMP(7);
+        if (cur_nb >= 0) flush(cur_nb);
+        BT_STAMP(12);
+    }
+    __syncthreads();
+    BT_STAMP(9);
+    BT_STAMP_CTA(3);
+    if (s_abort) {
+        if (tid == 0) {
+            // Give copies that may still be in flight a bounded chance to land before the
+            // shared memory is released.
+            for (int s = 0; s < stages && s < n_iters; ++s) {
+                const int last_it = ((n_iters - 1 - s) / stages) * stages + s;
+                mbar_wait_bounded(&s_full[s], (last_it / stages) & 1, 1u << 16);
+            }
+        }
+        return;
+    }
+    // epilogue: one thread per (row, column) of this CTA's column blocks, columns fastest
+    const int cols = nbl * TILE_N;
+    for (int m = 0; m < p.M; ++m)
+        for (int c = tid; c < cols; c += GT_THREADS) {
+            const int n = nb0 * TILE_N + c;
+            if (n >= p.N) continue;
+            int acc = -s_rowsum[m];
+#pragma unroll
+            for (int w = 0; w < GT_CONSUMER_WARPS; ++w) acc += s_part[(w * p.nbl_max * TILE_N + c) * MR + m];
+            if (p.acc_out != nullptr) p.acc_out[static_cast<int64_t>(m) * p.N + n] = acc;
+            const float y = dequant(acc, s_sx[m], s_scale[c], s_bias[c], p.bias != nullptr);
+            store_out_dt(p.Y, p.y_dtype, static_cast<int64_t>(m) * p.ldy + n, y);
+        }
+    BT_STAMP(13);
+}
+
+// ---- host side ------------------------------------------------------------------------------
+
+static size_t gemv_tiled_smem(int mr, int k_pad, int nbl_max, int stages) {
+    return static_cast<size_t>(stages) * GT_STAGE_BYTES + static_cast<size_t>(mr) * (k_pad + GT_X_PAD) +
+           sizeof(int) * (static_cast<size_t>(GT_CONSUMER_WARPS) * nbl_max * TILE_N * mr + mr + 2 * GT_CONSUMER_WARPS * mr + mr +
+                          2 * static_cast<size_t>(nbl_max) * TILE_N) +
+           sizeof(uint64_t) * (2 * stages + 1);
+}
+
+// Rows of activations one launch can hold as int8 in shared memory next to the ring.
+static int gemv_tiled_rows_per_launch(int64_t K) {
+    const int64_t k_pad = ceil_div<int64_t>(K, TILE_K) * TILE_K + GT_X_PAD;
+    int rows = GT_MAX_ROWS;
+    while (rows > 1 && rows * k_pad > 96 * 1024) rows >>= 1;
+    return rows;
+}
+
+template <int MR, bool FUSED>
+static int launch_gemv_tiled_kernel(const GemvTiledParams& p, int grid, size_t smem, cudaStream_t st) {
+    auto kern = gemv_tiled_kernel<MR, FUSED>;
+    if (smem > 48 * 1024)
+        BT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(GT_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attrs[1];
+    attrs[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attrs;
+    cfg.numAttrs = 1;
+    BT_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, p));
+    return BT_OK;
+}
+
+// One launch over `p.M` <= GT_MAX_ROWS rows.
+static int launch_gemv_tiled_rows(GemvTiledParams p, cudaStream_t st) {
+    p.KT = ceil_div(p.K, TILE_K);
+    p.NB = ceil_div(p.N, TILE_N);
+    const int mr = (p.M <= 1) ? 1 : (p.M <= 2) ? 2 : (p.M <= 4) ? 4 : 8;
+    // one CTA per SM; more CTAs only when a CTA's partial-sum slots would outgrow their budget
+    const int nbl_cap = std::max(1, GT_SLOT_BUDGET / mr);
+    const int grid = std::max(std::min(p.NB, sm_count()), ceil_div(p.NB, nbl_cap));
+    p.nbl_max = ceil_div(p.NB, grid);
+    const int max_tiles = p.nbl_max * p.KT;
+    p.stages = std::max(1, std::min(GT_MAX_STAGES, ceil_div(max_tiles, GT_STAGE_TILES)));
+    const size_t smem = gemv_tiled_smem(mr, p.KT * TILE_K, p.nbl_max, p.stages);
+    BT_UNSUPPORTED_IF(smem > 227 * 1024, "gemv_tiled: needs %zu bytes of shared memory (K too large)", smem);
+    const bool fused = p.X != nullptr;
+#define BT_GEMV_CASE(MRV)                                                                       \
+    if (mr == MRV)                                                                              \
+        return fused ? launch_gemv_tiled_kernel<MRV, true>(p, grid, smem, st) : launch_gemv_tiled_kernel<MRV, false>(p, grid, smem, st);
+    BT_GEMV_CASE(1)
+    BT_GEMV_CASE(2)
+    BT_GEMV_CASE(4)
+    BT_GEMV_CASE(8)
+#undef BT_GEMV_CASE
+    return BT_ERR_INVALID;
+}
+
+// Splits M rows into launches of at most gemv_tiled_rows_per_launch(K) rows over the same weights.
+static int launch_gemv_tiled(const GemvTiledParams& p, cudaStream_t st) {
+    const int rows = gemv_tiled_rows_per_launch(p.K);
+    for (int m0 = 0; m0 < p.M; m0 += rows) {
+        GemvTiledParams q = p;
+        q.M = std::min(rows, p.M - m0);
+        if (p.X != nullptr) q.X = static_cast<const char*>(p.X) + static_cast<size_t>(m0) * p.ldx * dtype_size(p.x_dtype);
+        if (p.Xq != nullptr) q.Xq = p.Xq + static_cast<int64_t>(m0) * p.K;
+        if (p.sx != nullptr) q.sx = p.sx + m0;
+        if (p.xq_out != nullptr) q.xq_out = p.xq_out + static_cast<int64_t>(m0) * p.K;
+        if (p.sx_out != nullptr) q.sx_out = p.sx_out + m0;
+        if (p.acc_out != nullptr) q.acc_out = p.acc_out + static_cast<int64_t>(m0) * p.N;
+        q.Y = static_cast<char*>(p.Y) + static_cast<size_t>(m0) * p.ldy * dtype_size(p.y_dtype);
+        const int rc = launch_gemv_tiled_rows(q, st);
+        if (rc != BT_OK) return rc;
+    }
+    return BT_OK;
+}
+
+static int check_gemv_tiled_args(const char* who, int64_t M, int64_t K, const uint8_t* tiled, int64_t N, const float* scale,
+                                 void* Y, int y_dtype, int64_t ldy) {
+    BT_REQUIRE(tiled && scale && Y, "%s: NULL pointer", who);
+    BT_REQUIRE(M > 0 && K > 0 && N > 0, "%s: X is empty or weight is empty", who);
+    BT_REQUIRE(valid_dtype(y_dtype), "%s: unknown output dtype %d", who, y_dtype);
+    BT_REQUIRE(ldy >= N, "%s: output row stride %lld < N %lld", who, (long long)ldy, (long long)N);
+    BT_REQUIRE(aligned(tiled, 16), "%s: tiled weights must be 16-byte aligned", who);
+    BT_UNSUPPORTED_IF(M > BT_GEMV_MAX_M, "%s: M=%lld exceeds %d", who, (long long)M, BT_GEMV_MAX_M);
+    BT_UNSUPPORTED_IF(K > BT_MAX_K, "%s: K=%lld exceeds %d", who, (long long)K, BT_MAX_K);
+    BT_UNSUPPORTED_IF(N > (int64_t{1} << 30), "%s: N too large", who);
+    return BT_OK;
+}
+
+static GemvTiledParams base_tiled_params(int64_t M, int64_t K, const uint8_t* tiled, int64_t N, const float* scale,
+                                         const float* bias, void* Y, int y_dtype, int64_t ldy, int32_t* acc_out) {
+    GemvTiledParams p = {};
+    p.W = tiled; p.scale = scale; p.bias = bias; p.Y = Y; p.acc_out = acc_out; p.ldy = ldy;
+    p.M = static_cast<int>(M); p.K = static_cast<int>(K); p.N = static_cast<int>(N);
+    p.y_dtype = y_dtype; p.x_dtype = BT_F32;
+    return p;
+}
+
+}  // namespace bt
+
+extern "C" int bt_gemv_tiled_i8(const int8_t* Xq, const float* sx, int64_t M, int64_t K, const uint8_t* tiled,
+                                int64_t N, const float* scale, const float* bias, void* Y, int y_dtype, int64_t ldy,
+                                int32_t* acc_out, void* stream) {
+    using namespace bt;
+    BT_REQUIRE(Xq != nullptr && sx != nullptr, "bt_gemv_tiled_i8: NULL pointer");
+    int rc = check_gemv_tiled_args("bt_gemv_tiled_i8", M, K, tiled, N, scale, Y, y_dtype, ldy);
+    if (rc != BT_OK) return rc;
+    GemvTiledParams p = base_tiled_params(M, K, tiled, N, scale, bias, Y, y_dtype, ldy, acc_out);
+    p.Xq = Xq; p.sx = sx;
+    p.x_vec = (K % 16 == 0) && aligned(Xq, 16);
+    return launch_gemv_tiled(p, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int bt_gemv_tiled(const void* X, int x_dtype, int64_t M, int64_t K, int64_t ldx, const uint8_t* tiled,
+                             int64_t N, const float* scale, const float* bias, void* Y, int y_dtype, int64_t ldy,
+                             int8_t* xq_out, float* sx_out, int32_t* acc_out, void* stream) {
+    using namespace bt;
+    BT_REQUIRE(X != nullptr, "bt_gemv_tiled: NULL pointer");
+    BT_REQUIRE(valid_dtype(x_dtype), "bt_gemv_tiled: unknown activation dtype %d", x_dtype);
+    BT_REQUIRE(ldx >= K, "bt_gemv_tiled: row stride %lld < K %lld", (long long)ldx, (long long)K);
+    int rc = check_gemv_tiled_args("bt_gemv_tiled", M, K, tiled, N, scale, Y, y_dtype, ldy);
+    if (rc != BT_OK) return rc;
+    GemvTiledParams p = base_tiled_params(M, K, tiled, N, scale, bias, Y, y_dtype, ldy, acc_out);
+    p.X = X; p.x_dtype = x_dtype; p.ldx = ldx; p.xq_out = xq_out; p.sx_out = sx_out;
+    p.x_vec = (K % 4 == 0) && (ldx % 4 == 0) && aligned(X, 4 * dtype_size(x_dtype));
+    return launch_gemv_tiled(p, static_cast<cudaStream_t>(stream));
+}

@@ -2,6 +2,7 @@
 // Every kernel file is a header included here, so device globals have one definition
 // and no relocatable device code is needed.
 #include <algorithm>
+#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
@@ -34,6 +35,7 @@ int sm_count() {
 #include "act_quant.cuh"
 #include "gemm_tcgen05.cuh"
 #include "gemv.cuh"
+#include "gemv_tiled.cuh"
 #include "linear_float.cuh"
 #include "quantize_pack.cuh"
 #include "retile.cuh"
@@ -64,3 +66,20 @@ extern "C" int bt_dummy(const void* src, void* dst, size_t bytes, void* stream) 
     BT_CUDA_OK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(stream)));
     return BT_OK;
 }
+
+#ifdef BT_TRACE
+// Bring-up aid (only in -DBT_TRACE builds): copies the kernel timeline stamps to the host.
+extern "C" int bt_trace_read(unsigned long long* out64) {
+    using namespace bt;
+    BT_CUDA_OK(cudaDeviceSynchronize());
+    BT_CUDA_OK(cudaMemcpyFromSymbol(out64, g_trace, sizeof(unsigned long long) * 128));
+    return BT_OK;
+}
+extern "C" int bt_trace_read_cta(unsigned long long* out64, unsigned int* sm) {
+    using namespace bt;
+    BT_CUDA_OK(cudaDeviceSynchronize());
+    BT_CUDA_OK(cudaMemcpyFromSymbol(out64, g_trace_cta, sizeof(unsigned long long) * 4096 * 4));
+    BT_CUDA_OK(cudaMemcpyFromSymbol(sm, g_trace_sm, sizeof(unsigned int) * 4096));
+    return BT_OK;
+}
+#endif

@@ -1,23 +1,34 @@
 // Private "tiled" layout of the packed weights and its conversion kernels.
 //
 // The buffer is an array of 512-byte tiles, tile (nb, kt) at ((nb*KT)+kt)*512 with
-// KT = ceil(K/32): 64 output columns x 32 inputs, so the tiles of one column block
-// are contiguous along K and a K slice is a single bulk copy.  Inside a tile, lane
+// KT = ceil(K/128): 16 output columns x 128 inputs, so the tiles of one 16-column block
+// are contiguous along K (a whole column block is one bulk copy).  Inside a tile, lane
 // l = 4g+t of a warp owns 16 bytes = words q=0..3; byte j of word q holds four 2-bit
 // fields, field i (bits 2i+1:2i) being the weight
-//     n = 64 nb + 16 i + g + 8 (q & 1),     k = 32 kt + 16 (q >> 1) + 4 t + j
+//     n = 16 nb + g + 8 (q & 1),     k = 128 kt + 32 t + 8 i + 4 (q >> 1) + j
 // stored as t+1 in {0,1,2} (padding outside N x K is 1, i.e. a zero weight).
-// Masking plane i of the four words (w & (0x03030303 << 2i)) therefore yields the
-// A fragment (a0..a3) of an m16n8k32 MMA for columns 16i..16i+15, scaled by 4^i.
+// So masking plane i of word q (w & (0x03030303 << 2i)) yields four consecutive k of one
+// column as bytes scaled by 4^i — a dp4a operand for the decode kernel — and a lane's
+// eight (plane, word-half) pieces cover 32 consecutive activations.  For the tensor-core
+// kernel, (w >> 2i) & 0x03030303 is four bytes of row n of a K-major 128-byte operand row.
 #pragma once
 
 #include "common.cuh"
 
 namespace bt {
 
-constexpr int TILE_N = 64;
-constexpr int TILE_K = 32;
+constexpr int TILE_N = 16;
+constexpr int TILE_K = 128;
 constexpr int TILE_BYTES = 512;
+
+// Position of weight (n_local, k_local) inside a tile: 32-bit word index and bit shift.
+__host__ __device__ inline void tile_slot(int n_local, int k_local, int& word, int& shift) {
+    const int g = n_local & 7, qlo = n_local >> 3;
+    const int t = k_local >> 5, r = k_local & 31;
+    const int i = r >> 3, qhi = (r >> 2) & 1, j = r & 3;
+    word = (4 * g + t) * 4 + (qlo | (qhi << 1));
+    shift = 8 * j + 2 * i;
+}
 
 // grid = (KT, NB), block = 128: one thread per 32-bit word of the tile.
 __global__ void __launch_bounds__(128)
@@ -26,11 +37,12 @@ retile_kernel(const uint8_t* __restrict__ packed_T, int K, int N, int KT, uint8_
     const int lane = threadIdx.x >> 2, q = threadIdx.x & 3;
     const int g = lane >> 2, t = lane & 3;
     const int KB = (K + 3) / 4;
-    const int kb = 8 * kt + 4 * (q >> 1) + t;          // public row: holds k = 4kb .. 4kb+3
+    const int n = TILE_N * nb + g + 8 * (q & 1);
     uint32_t word = 0;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        const int n = TILE_N * nb + 16 * i + g + 8 * (q & 1);
+        // public row kb holds k = 4kb .. 4kb+3 of every column
+        const int kb = (TILE_K * kt + 32 * t + 8 * i + 4 * (q >> 1)) >> 2;
         uint32_t byte = 0;
         if (n < N && kb < KB) byte = packed_T[static_cast<int64_t>(kb) * N + n];
 #pragma unroll
@@ -51,17 +63,16 @@ __global__ void untile_kernel(const uint8_t* __restrict__ tiled, int K, int N, i
     for (int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; idx < total;
          idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
         const int kb = static_cast<int>(idx / N), n = static_cast<int>(idx % N);
-        const int nb = n / TILE_N, nl = n % TILE_N;
-        const int i = nl / 16, r = nl % 16, g = r % 8, qlo = r / 8;
-        const int kt = kb / 8, kbl = kb % 8, qhi = kbl / 4, t = kbl % 4;
-        const int q = qlo | (qhi << 1);
+        const int nb = n / TILE_N, kt = (4 * kb) / TILE_K;
         const int64_t tile = static_cast<int64_t>(nb) * KT + kt;
-        const uint32_t word = reinterpret_cast<const uint32_t*>(tiled + tile * TILE_BYTES)[(4 * g + t) * 4 + q];
+        const uint32_t* words = reinterpret_cast<const uint32_t*>(tiled + tile * TILE_BYTES);
         uint32_t byte = 0;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int k = 4 * kb + j;
-            const int tv = static_cast<int>((word >> (8 * j + 2 * i)) & 3u) - 1;
+            int word, shift;
+            tile_slot(n % TILE_N, k % TILE_K, word, shift);
+            const int tv = static_cast<int>((words[word] >> shift) & 3u) - 1;
             const uint32_t c = (k < K) ? (tv == 1 ? 1u : (tv == -1 ? 2u : 0u)) : 0u;
             byte |= c << (2 * j);
         }

@@ -102,15 +102,18 @@ int bt_unpack_codes(const uint8_t* packed_T, int64_t N, int64_t K, int8_t* codes
  * Replaces the in-kernel quantizer of the reference's integer kernel
  * (csrc/kernels/ternary_gemm_tensor_core.cu:343-347, 424-459), applied per row as
  * that file's header specifies (:16-18).
- * X [M,K] row stride ldx, dtype x_dtype; Xq int8 [M,K]; sx float32 [M].
+ * X [M,K] row stride ldx, dtype x_dtype; Xq int8 [M,K]; sx float32 [M];
+ * xsum int32 [M] (optional): per-row sums of the int8 codes, an input of
+ * bt_gemm_tiled_i8 (which multiplies weights stored as t+1).
  */
 int bt_act_quant_i8(const void* X, int x_dtype, int64_t M, int64_t K, int64_t ldx,
-                    int8_t* Xq, float* sx, void* stream);
+                    int8_t* Xq, float* sx, int32_t* xsum, void* stream);
 
 /*
  * Private streaming layout of the packed weights ("tiled"): still 2 bits per
- * weight, re-ordered into 512-byte tiles of 64 output columns x 32 inputs so that
- * one 16-byte load per lane is a ready-made tensor-core operand.  It is a derived
+ * weight, re-ordered into 512-byte tiles of 16 output columns x 128 inputs, the
+ * tiles of a column block contiguous along K, so that a column block is one bulk
+ * copy and one 16-byte load per lane yields ready-made dp4a operands.  It is a derived
  * cache of the public [ceil(K/4),N] buffer and round-trips to it bit for bit.
  * (No counterpart in the reference; the public buffer stays the wire format of
  * TernaryLinearInference.weight_packed, bittorch/nn/ternary_linear_infer.py:68-73.)
@@ -140,14 +143,34 @@ int bt_gemv_tiled_i8(const int8_t* Xq, const float* sx, int64_t M, int64_t K,
                      void* Y, int y_dtype, int64_t ldy, int32_t* acc_out, void* stream);
 
 /*
+ * Decode-size packed ternary linear straight from floating-point activations: the
+ * per-token int8 quantizer of bt_act_quant_i8 runs inside the GEMV kernel (each CTA
+ * reduces |x| over its K slice, the thread-block cluster exchanges the partial maxima),
+ * so a decode layer is ONE dependent kernel launch.  Results are bit-identical to
+ * bt_act_quant_i8 followed by bt_gemv_tiled_i8.
+ * Replaces the quantize-inside-the-GEMM structure of the reference's integer kernel
+ * (csrc/kernels/ternary_gemm_tensor_core.cu:396-459) for small batches.
+ *
+ * X [M,K] row stride ldx, dtype x_dtype, M <= BT_GEMV_MAX_M; other arguments as
+ * bt_gemv_tiled_i8.  xq_out int8 [M,K] and sx_out float32 [M] (both optional) receive
+ * the quantized activations the kernel used (parity checks).
+ */
+int bt_gemv_tiled(const void* X, int x_dtype, int64_t M, int64_t K, int64_t ldx,
+                  const uint8_t* tiled, int64_t N, const float* scale, const float* bias,
+                  void* Y, int y_dtype, int64_t ldy, int8_t* xq_out, float* sx_out,
+                  int32_t* acc_out, void* stream);
+
+/*
  * Prefill-size packed ternary linear on int8 activations (any M >= 1), same
  * arithmetic as above, contraction on the 5th-generation tensor cores
  * (tcgen05.mma kind::i8, accumulators in tensor memory).  Reads the tiled layout.
  * Replaces ternary_linear_packed_forward for large batches
  * (csrc/kernels/ternary_gemm_production.cu:158-250) and the experimental
  * mma.sync kernel (csrc/kernels/ternary_gemm_tensor_core.cu:349-657).
+ * xsum int32 [M]: per-row sums of Xq, as written by bt_act_quant_i8 (required).
+ * K must be a multiple of 16 (row pitch of the TMA descriptor over Xq).
  */
-int bt_gemm_tiled_i8(const int8_t* Xq, const float* sx, int64_t M, int64_t K,
+int bt_gemm_tiled_i8(const int8_t* Xq, const float* sx, const int32_t* xsum, int64_t M, int64_t K,
                      const uint8_t* tiled, int64_t N, const float* scale, const float* bias,
                      void* Y, int y_dtype, int64_t ldy, int32_t* acc_out, void* stream);
 

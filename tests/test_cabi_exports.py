@@ -31,7 +31,7 @@ def test_library_exports_every_declared_symbol():
     lib.bt_tiled_bytes.restype = ctypes.c_size_t
     lib.bt_tiled_bytes.argtypes = [ctypes.c_int64, ctypes.c_int64]
     assert lib.bt_tiled_bytes(4096, 4096) == 4096 * 4096 // 4          # still 2 bits per weight
-    assert lib.bt_tiled_bytes(33, 65) == 2 * 2 * 512                    # padded to 64 x 32 tiles
+    assert lib.bt_tiled_bytes(33, 65) == 5 * 1 * 512                    # padded to 16 x 128 tiles
     assert lib.bt_tiled_bytes(0, 5) == 0
 
 
@@ -47,8 +47,8 @@ def test_argument_errors_come_back_as_codes_not_crashes():
     lib = ctypes.CDLL(_build.build())
     lib.bt_last_error.restype = ctypes.c_char_p
     i64, p = ctypes.c_int64, ctypes.c_void_p
-    lib.bt_act_quant_i8.argtypes = [p, ctypes.c_int, i64, i64, i64, p, p, p]
-    assert lib.bt_act_quant_i8(None, 0, 1, 1, 1, None, None, None) == 1          # BT_ERR_INVALID
+    lib.bt_act_quant_i8.argtypes = [p, ctypes.c_int, i64, i64, i64, p, p, p, p]
+    assert lib.bt_act_quant_i8(None, 0, 1, 1, 1, None, None, None, None) == 1          # BT_ERR_INVALID
     assert b"NULL" in lib.bt_last_error()
     lib.bt_quantize_pack.argtypes = [p, ctypes.c_int, i64, i64, i64, ctypes.c_float, p, p, p, p, p]
     assert lib.bt_quantize_pack(p(16), 7, 4, 4, 4, 0.05, None, p(16), None, None, None) == 1
@@ -60,8 +60,8 @@ def test_argument_errors_come_back_as_codes_not_crashes():
     assert b"exceeds" in lib.bt_last_error()
     assert lib.bt_gemv_tiled_i8(p(16), p(16), 0, 64, p(16), 64, p(16), None, p(16), 0, 64, None, None) == 1
     assert b"empty" in lib.bt_last_error()
-    lib.bt_gemm_tiled_i8.argtypes = lib.bt_gemv_tiled_i8.argtypes
-    assert lib.bt_gemm_tiled_i8(p(16), p(16), 32, 40, p(16), 64, p(16), None, p(16), 0, 64, None, None) == 3
+    lib.bt_gemm_tiled_i8.argtypes = [p, p, p, i64, i64, p, i64, p, p, p, ctypes.c_int, i64, p, p]
+    assert lib.bt_gemm_tiled_i8(p(16), p(16), p(16), 32, 40, p(16), 64, p(16), None, p(16), 0, 64, None, None) == 3
     assert b"multiple of 16" in lib.bt_last_error()
 
 

@@ -149,3 +149,80 @@ def test_gemm_full_size_properties():
     y_shard = _C.gemm_tiled_i8(xq, sx, shard, k, 2752, scale[2752:5504].contiguous(), None, torch.float32)
     assert torch.equal(y_shard, y[:, 2752:5504])
     assert _C.device_status() == 0
+
+
+FUSED_SHAPES = [(1, 4096, 4096), (1, 4096, 11008), (2, 4096, 4096), (3, 2560, 6912), (4, 4096, 11008), (7, 33, 17),
+                (8, 1024, 640), (1, 1, 1), (16, 4096, 4096), (9, 8192, 1024), (5, 100, 300), (13, 48, 200),
+                (1, 28672, 256), (16, 65, 129)]
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32, torch.float16])
+@pytest.mark.parametrize("m,k,n", FUSED_SHAPES)
+def test_gemv_fused_quantizer_bit_exact(oracle, m, k, n, dtype):
+    """One-kernel decode layer (activation quantizer inside the GEMV): int8 activations,
+    row scales, int32 accumulators and outputs all equal the oracle's, bit for bit."""
+    from bittorch_b200 import _C
+
+    g = torch.Generator().manual_seed(m * 7 + k + n)
+    codes = torch.randint(-1, 2, (n, k), generator=g, dtype=torch.int8)
+    x = (torch.randn(m, k, generator=g) * 2.5).to(dtype)
+    scale = torch.rand(n, generator=g) + 0.1
+    bias = torch.randn(n, generator=g)
+    tiled = _C.retile(_C.pack_codes(codes.cuda()), k)
+    y, xq, sx, acc = _C.gemv_tiled(x.cuda(), tiled, k, n, scale.cuda(), bias.cuda(), want_debug=True)
+    torch.cuda.synchronize()
+    assert _C.device_status() == 0
+    q_ref, sx_ref = oracle.act_quant(x.float().numpy())
+    acc_ref = oracle.gemm_i32(q_ref, codes.numpy())
+    y_ref = oracle.epilogue(acc_ref, sx_ref, scale.numpy(), bias.numpy())
+    assert np.array_equal(xq.cpu().numpy(), q_ref)
+    assert np.array_equal(sx.cpu().numpy().view(np.uint32), sx_ref.view(np.uint32))
+    assert np.array_equal(acc.cpu().numpy(), acc_ref)
+    assert torch.equal(y.cpu(), torch.from_numpy(y_ref).to(dtype))
+
+
+@pytest.mark.parametrize("split", ["1", "2", "4", "8"])
+def test_public_layout_every_k_split_gives_the_same_bits(oracle, split, monkeypatch):
+    """The compatibility kernel splits K over a thread-block cluster; every split size must
+    produce the oracle's accumulators."""
+    from bittorch_b200 import _C
+
+    monkeypatch.setenv("BITTORCH_B200_GEMV_SPLIT", split)
+    for (m, k, n) in [(1, 4096, 1024), (6, 1000, 200), (16, 2048, 512)]:
+        prob = _problem(m, k, n, seed=int(split) + m)
+        acc_ref, y_ref = _reference(oracle, *prob)
+        y, acc = _run("gemv_packed_i8", *prob, torch.float32, tiled=False)
+        assert np.array_equal(acc.numpy(), acc_ref)
+        assert np.array_equal(y.numpy().view(np.uint32), y_ref.view(np.uint32))
+
+
+def test_fused_and_two_kernel_paths_agree(oracle):
+    from bittorch_b200 import _C
+
+    for (m, k, n) in [(1, 4096, 1024), (6, 1000, 200), (16, 2048, 512), (11, 28672, 64)]:
+        g = torch.Generator().manual_seed(m)
+        codes = torch.randint(-1, 2, (n, k), generator=g, dtype=torch.int8)
+        x = torch.randn(m, k, generator=g).to(torch.bfloat16).cuda()
+        scale = (torch.rand(n, generator=g) + 0.1).cuda()
+        tiled = _C.retile(_C.pack_codes(codes.cuda()), k)
+        y = _C.gemv_tiled(x, tiled, k, n, scale, None)
+        xq, sx = _C.act_quant_i8(x)
+        assert torch.equal(y, _C.gemv_tiled_i8(xq, sx, tiled, k, n, scale, None, torch.bfloat16))
+    assert _C.device_status() == 0
+
+
+def test_gemv_fused_strided_rows(oracle):
+    """Activations that are a column slice of a wider matrix (row stride > K)."""
+    from bittorch_b200 import _C
+
+    g = torch.Generator().manual_seed(21)
+    k, n = 512, 384
+    codes = torch.randint(-1, 2, (n, k), generator=g, dtype=torch.int8)
+    wide = torch.randn(4, 1408, generator=g).to(torch.bfloat16).cuda()
+    x = wide[:, :k]
+    scale = (torch.rand(n, generator=g) + 0.1).cuda()
+    tiled = _C.retile(_C.pack_codes(codes.cuda()), k)
+    y, xq, sx, acc = _C.gemv_tiled(x, tiled, k, n, scale, None, want_debug=True)
+    q_ref, sx_ref = oracle.act_quant(x.float().cpu().numpy())
+    assert np.array_equal(xq.cpu().numpy(), q_ref)
+    assert np.array_equal(acc.cpu().numpy(), oracle.gemm_i32(q_ref, codes.numpy()))
