@@ -145,7 +145,7 @@ def make_decode_step(stack: LayerStack, m: int, x0: torch.Tensor, group=None):
     y_loc = [torch.empty((m, nl), dtype=torch.bfloat16, device=dev) for _ in range(stack.layers)]
     y_all = [torch.empty((world * m, nl), dtype=torch.bfloat16, device=dev) for _ in range(stack.layers)] if world > 1 else None
     lib, stream_of = _C._lib, _C._stream
-    fused = m <= _C.GEMV_MAX_M          # decode: activation quantizer inside the GEMV kernel
+    fused = m <= _C.DECODE_MAX_M        # decode: activation quantizer inside the GEMV kernel
     fn = lib.bt_gemm_tiled_i8
 
     def step():
@@ -224,7 +224,7 @@ def time_kernel_only(stack: LayerStack, m: int, reps: int = 20) -> float:
     def run():
         st = _C._stream(xq)
         for l in range(stack.layers):
-            if m <= _C.GEMV_MAX_M:      # the decode kernel, activation quantizer included
+            if m <= _C.DECODE_MAX_M:    # the decode kernel, activation quantizer included
                 _C._check(lib.bt_gemv_tiled(x.data_ptr(), _C.BT_BF16, m, stack.k, stack.k, stack.tiled[l].data_ptr(),
                                             stack.n_local, stack.scale[l].data_ptr(), None, y.data_ptr(), _C.BT_BF16,
                                             stack.n_local, None, None, None, st))
@@ -399,11 +399,11 @@ def run_sweep(peaks, dev):
         for m in (1, 4, 16, 256, 2048):
             ms = time_kernel_only(stack, m, reps=10 if m <= 16 else 3)
             row = {"K": k, "N": n, "M": m, "us": ms * 1e3}
-            if m <= 16:
+            if m <= 16:     # decode sizes are judged on bytes streamed
                 gbs = algorithmic_bytes(m, k, n) / (ms * 1e-3) / 1e9
-                row.update({"kernel": "gemv_tiled", "gbs": gbs, "frac_hbm_measured": gbs / peaks["hbm_gbs"],
-                            "frac_hbm_nominal_8tbs": gbs / 8000.0})
-            else:
+                row.update({"kernel": "gemv_tiled" if m <= 4 else "gemm_tcgen05", "gbs": gbs,
+                            "frac_hbm_measured": gbs / peaks["hbm_gbs"], "frac_hbm_nominal_8tbs": gbs / 8000.0})
+            if m > 4:       # tensor-core sizes on integer operations
                 tops = 2.0 * m * n * k / (ms * 1e-3) / 1e12
                 row.update({"kernel": "gemm_tcgen05", "int8_tops": tops, "frac_int8_nominal_4500": tops / 4500.0,
                             "frac_int8_mm_proxy": tops / int8_proxy if int8_proxy == int8_proxy else None})

@@ -21,7 +21,8 @@ from torch import Tensor
 from . import _build
 
 BT_F32, BT_F16, BT_BF16 = 0, 1, 2
-GEMV_MAX_M = 16
+GEMV_MAX_M = 16          # largest batch the decode kernels accept
+DECODE_MAX_M = 4         # batches up to here run the decode kernel; above it the tensor-core kernel is faster
 _DT = {torch.float32: BT_F32, torch.float16: BT_F16, torch.bfloat16: BT_BF16}
 
 _p = ctypes.c_void_p
@@ -290,21 +291,23 @@ def gemm_tiled_i8(xq, sx, tiled, in_features, out_features, scale, bias=None, ou
 
 def int8_linear_tiled(x2d: Tensor, tiled: Tensor, in_features: int, out_features: int, scale: Tensor,
                       bias: Optional[Tensor]) -> Tensor:
-    """Activation quantizer + the kernel that fits M: GEMV for M <= 16, tcgen05 GEMM above.
+    """The integer path for any batch: one fused quantize+GEMV kernel for M <= DECODE_MAX_M
+    (its dp4a arithmetic grows with M), activation quantizer + tcgen05 GEMM above (cost
+    almost flat in M up to a full 128-row tile).
 
     K that is not a multiple of 16 cannot be described to the TMA engine; such ragged
     shapes go through the decode kernel in chunks of 16 rows.
     """
     m = x2d.shape[0]
-    if m <= GEMV_MAX_M:
+    if m <= DECODE_MAX_M:
         return gemv_tiled(x2d, tiled, in_features, out_features, scale, bias)
-    xq, sx, xsum = act_quant_i8(x2d, want_sum=True)
     if in_features % 16 == 0:
+        xq, sx, xsum = act_quant_i8(x2d, want_sum=True)
         return gemm_tiled_i8(xq, sx, tiled, in_features, out_features, scale, bias, x2d.dtype, xsum=xsum)
     y = torch.empty((m, out_features), dtype=x2d.dtype, device=x2d.device)
     for m0 in range(0, m, GEMV_MAX_M):
         m1 = min(m, m0 + GEMV_MAX_M)
-        gemv_tiled_i8(xq[m0:m1], sx[m0:m1], tiled, in_features, out_features, scale, bias, x2d.dtype, out=y[m0:m1])
+        gemv_tiled(x2d[m0:m1], tiled, in_features, out_features, scale, bias, out=y[m0:m1])
     return y
 
 
@@ -405,7 +408,7 @@ def _packed_forward(X: Tensor, W_T: Tensor, scale: Tensor, bias: Optional[Tensor
         with torch.cuda.device(X.device):
             _check(_lib.bt_linear_packed_float(_ptr(x2d), _dtype_code(x2d, "X"), m, k, _ptr(w), n, _ptr(s32), _ptr(b32),
                                                _ptr(y), _stream(x2d)))
-    elif m <= GEMV_MAX_M:
+    elif m <= DECODE_MAX_M:
         xq, sx = act_quant_i8(x2d)
         y = gemv_packed_i8(xq, sx, w, k, s32, b32, X.dtype)
     else:

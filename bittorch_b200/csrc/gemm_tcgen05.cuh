@@ -25,18 +25,41 @@
 namespace bt {
 
 constexpr int GM_BM = 128;
-constexpr int GM_BN = 256;
 constexpr int GM_BK = 128;                       // bytes = int8 elements per K block
-constexpr int GM_STAGES = 3;
-constexpr int GM_A_BYTES = GM_BM * GM_BK;        // 16 KB
-constexpr int GM_B_BYTES = GM_BN * GM_BK;        // 32 KB
-constexpr int GM_P_TILES = (GM_BN / TILE_N) * (GM_BK / TILE_K);             // 16 column blocks x 1 k tile
-constexpr int GM_P_BYTES = GM_P_TILES * TILE_BYTES;                          // 8 KB of packed tiles
+constexpr int GM_A_BYTES = GM_BM * GM_BK;        // 16 KB activation tile
 constexpr int GM_UNPACK_WARPS = 8;
+constexpr int GM_UNPACK_GROUPS = 2;              // groups of unpack warps that work on alternate K blocks
+constexpr int GM_GROUP_WARPS = GM_UNPACK_WARPS / GM_UNPACK_GROUPS;
 constexpr int GM_EPI_WARPS = 4;
 constexpr int GM_THREADS = (2 + GM_EPI_WARPS + GM_UNPACK_WARPS) * 32;          // 448
-constexpr int GM_TMEM_COLS = 512;
-constexpr size_t GM_SMEM_BYTES = 1024 /*alignment slack*/ + GM_STAGES * (GM_A_BYTES + GM_B_BYTES + GM_P_BYTES) + 256;
+
+// Per output-tile width BN: the load ring (activation tile + 2-bit weight tiles, filled by
+// TMA) is deep because its latency is a global-memory round trip, the ring of unpacked
+// weight tiles is shallow because it is filled from shared memory.
+template <int BN> struct GemmCfg;
+template <> struct GemmCfg<256> { static constexpr int NL = 5, NB = 3; };
+template <> struct GemmCfg<128> { static constexpr int NL = 6, NB = 4; };
+template <> struct GemmCfg<64> { static constexpr int NL = 8, NB = 4; };
+
+template <int BN> __host__ __device__ constexpr int gm_p_tiles() { return BN / TILE_N; }                 // packed tiles per stage
+template <int BN> __host__ __device__ constexpr int gm_p_bytes() { return gm_p_tiles<BN>() * TILE_BYTES; }
+template <int BN> __host__ __device__ constexpr int gm_b_bytes() { return BN * GM_BK; }
+template <int BN> constexpr size_t gm_smem_bytes() {
+    return 1024 /*alignment slack*/ + static_cast<size_t>(GemmCfg<BN>::NL) * (GM_A_BYTES + gm_p_bytes<BN>()) +
+           static_cast<size_t>(GemmCfg<BN>::NB) * gm_b_bytes<BN>() + 512;
+}
+
+// Position in a ring of mbarrier-guarded stages (no divisions in the loops).
+struct RingPos {
+    int s = 0;
+    uint32_t phase = 0;
+    __device__ __forceinline__ void advance(int n) {
+        if (++s == n) { s = 0; phase ^= 1; }
+    }
+    __device__ __forceinline__ void advance_by(int n, int step) {
+        for (int i = 0; i < step; ++i) advance(n);
+    }
+};
 
 struct GemmParams {
     const uint8_t* tiled;
@@ -109,9 +132,10 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
     return d;
 }
 // Instruction descriptor: D = s32, A = s8 (activations), B = u8 (weight codes), both K-major,
-// M = 128, N = GM_BN.
-constexpr uint32_t GM_IDESC = (2u << 4) | (1u << 7) | (0u << 10) | (static_cast<uint32_t>(GM_BN >> 3) << 17) |
-                              (static_cast<uint32_t>(GM_BM >> 4) << 24);
+// M = 128, N = BN.
+template <int BN> __host__ __device__ constexpr uint32_t gm_idesc() {
+    return (2u << 4) | (1u << 7) | (0u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(GM_BM >> 4) << 24);
+}
 
 // Bounded mbarrier wait that also gives up when another role has already failed.
 __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
@@ -124,34 +148,42 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, vo
     return false;
 }
 
+template <int BN>
 __global__ void __launch_bounds__(GM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const GemmParams p) {
+    constexpr int NL = GemmCfg<BN>::NL, NB = GemmCfg<BN>::NB;
+    constexpr int P_TILES = gm_p_tiles<BN>(), P_BYTES = gm_p_bytes<BN>(), B_BYTES = gm_b_bytes<BN>();
+    constexpr uint32_t TMEM_COLS = 2 * BN;               // double-buffered accumulator (power of two >= 128)
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t* s_a = smem;
-    uint8_t* s_b = s_a + GM_STAGES * GM_A_BYTES;
-    uint8_t* s_p = s_b + GM_STAGES * GM_B_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(s_p + GM_STAGES * GM_P_BYTES);
-    uint64_t* full_load = bars;                      // [GM_STAGES] producer -> unpack, MMA
-    uint64_t* full_b = bars + GM_STAGES;             // [GM_STAGES] unpack -> MMA
-    uint64_t* empty = bars + 2 * GM_STAGES;          // [GM_STAGES] MMA -> producer
-    uint64_t* tmem_full = bars + 3 * GM_STAGES;      // [2] MMA -> epilogue
-    uint64_t* tmem_empty = tmem_full + 2;            // [2] epilogue -> MMA
+    uint8_t* s_a = smem;                                 // [NL] activation tiles, 128-byte swizzle
+    uint8_t* s_b = s_a + NL * GM_A_BYTES;                // [NB] unpacked weight tiles, 128-byte swizzle
+    uint8_t* s_p = s_b + NB * B_BYTES;                   // [NL] packed 2-bit tiles
+    uint64_t* bars = reinterpret_cast<uint64_t*>(s_p + NL * P_BYTES);
+    uint64_t* full_load = bars;                          // [NL] producer -> unpack, MMA
+    uint64_t* empty_load = full_load + NL;               // [NL] MMA -> producer
+    uint64_t* full_b = empty_load + NL;                  // [NB] unpack -> MMA
+    uint64_t* empty_b = full_b + NB;                     // [NB] MMA -> unpack
+    uint64_t* tmem_full = empty_b + NB;                  // [2] MMA -> epilogue
+    uint64_t* tmem_empty = tmem_full + 2;                // [2] epilogue -> MMA
     uint32_t* s_tmem = reinterpret_cast<uint32_t*>(tmem_empty + 2);
     __shared__ int s_abort_storage;
     volatile int* s_abort = &s_abort_storage;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m_tiles = (p.M + GM_BM - 1) / GM_BM;
-    const int n_tiles = (p.N + GM_BN - 1) / GM_BN;
+    const int n_tiles = (p.N + BN - 1) / BN;
     const int total_tiles = m_tiles * n_tiles;
     const int k_blocks = (p.K + GM_BK - 1) / GM_BK;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < GM_STAGES; ++s) {
+        for (int s = 0; s < NL; ++s) {
             mbar_init(&full_load[s], 1);
-            mbar_init(&full_b[s], GM_UNPACK_WARPS);
-            mbar_init(&empty[s], 1);
+            mbar_init(&empty_load[s], 1);
+        }
+        for (int s = 0; s < NB; ++s) {
+            mbar_init(&full_b[s], GM_GROUP_WARPS);
+            mbar_init(&empty_b[s], 1);
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(&tmem_full[a], 1);
@@ -160,7 +192,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const GemmParams 
         s_abort_storage = 0;
         mbar_fence_init();
     }
-    if (warp == 2) tmem_alloc(s_tmem, GM_TMEM_COLS);
+    if (warp == 2) tmem_alloc(s_tmem, TMEM_COLS);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -171,43 +203,47 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const GemmParams 
     if (warp == 0) {
         // ================= producer =================
         if (lane == 0) {
-            uint32_t it = 0;
+            RingPos ld;
             for (int tile = blockIdx.x; tile < total_tiles && !*s_abort; tile += gridDim.x) {
                 const int mt = tile % m_tiles, nt = tile / m_tiles;
-                const int nb0 = nt * (GM_BN / TILE_N);
-                const int nb_valid = min(GM_BN / TILE_N, p.NB - nb0);
-                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-                    const int s = it % GM_STAGES;
-                    if (!wait_or_abort(&empty[s], ((it / GM_STAGES) & 1) ^ 1, s_abort)) break;
-                    mbar_expect_tx(&full_load[s], GM_A_BYTES + static_cast<uint32_t>(nb_valid) * TILE_BYTES);
-                    tma_load_2d(s_a + s * GM_A_BYTES, &map_x, kb * GM_BK, mt * GM_BM, &full_load[s]);
+                const int nb0 = nt * P_TILES;
+                const int nb_valid = min(P_TILES, p.NB - nb0);
+                bool ok = true;
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!wait_or_abort(&empty_load[ld.s], ld.phase ^ 1, s_abort)) { ok = false; break; }
+                    mbar_expect_tx(&full_load[ld.s], GM_A_BYTES + static_cast<uint32_t>(nb_valid) * TILE_BYTES);
+                    tma_load_2d(s_a + ld.s * GM_A_BYTES, &map_x, kb * GM_BK, mt * GM_BM, &full_load[ld.s]);
                     for (int j = 0; j < nb_valid; ++j)      // one 512-byte tile per 16-column block
-                        bulk_g2s(s_p + s * GM_P_BYTES + j * TILE_BYTES,
-                                 p.tiled + (static_cast<int64_t>(nb0 + j) * p.KT + kb) * TILE_BYTES, TILE_BYTES, &full_load[s]);
+                        bulk_g2s(s_p + ld.s * P_BYTES + j * TILE_BYTES,
+                                 p.tiled + (static_cast<int64_t>(nb0 + j) * p.KT + kb) * TILE_BYTES, TILE_BYTES, &full_load[ld.s]);
+                    ld.advance(NL);
                 }
+                if (!ok) break;
             }
         }
     } else if (warp == 1) {
         // ================= MMA issuer =================
         if (lane == 0) {
-            uint32_t it = 0, tcount = 0;
+            RingPos ld, bb;
+            uint32_t tcount = 0;
             for (int tile = blockIdx.x; tile < total_tiles && !*s_abort; tile += gridDim.x, ++tcount) {
                 const uint32_t a = tcount & 1;
                 if (!wait_or_abort(&tmem_empty[a], ((tcount >> 1) & 1) ^ 1, s_abort)) break;
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + a * GM_BN;
+                const uint32_t d_tmem = tmem_base + a * BN;
                 bool ok = true;
-                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-                    const int s = it % GM_STAGES;
-                    const uint32_t ph = (it / GM_STAGES) & 1;
-                    if (!wait_or_abort(&full_load[s], ph, s_abort) || !wait_or_abort(&full_b[s], ph, s_abort)) { ok = false; break; }
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!wait_or_abort(&full_load[ld.s], ld.phase, s_abort) || !wait_or_abort(&full_b[bb.s], bb.phase, s_abort)) { ok = false; break; }
                     tc_fence_after();
-                    const uint64_t da = umma_desc_sw128(smem_u32(s_a + s * GM_A_BYTES));
-                    const uint64_t db = umma_desc_sw128(smem_u32(s_b + s * GM_B_BYTES));
+                    const uint64_t da = umma_desc_sw128(smem_u32(s_a + ld.s * GM_A_BYTES));
+                    const uint64_t db = umma_desc_sw128(smem_u32(s_b + bb.s * B_BYTES));
 #pragma unroll
                     for (int k = 0; k < GM_BK / 32; ++k)   // +32 bytes along K = +2 in the (>>4) address field
-                        umma_i8(d_tmem, da + 2 * k, db + 2 * k, GM_IDESC, (kb > 0 || k > 0) ? 1u : 0u);
-                    umma_commit(&empty[s]);
+                        umma_i8(d_tmem, da + 2 * k, db + 2 * k, gm_idesc<BN>(), (kb > 0 || k > 0) ? 1u : 0u);
+                    umma_commit(&empty_load[ld.s]);        // frees the activation + packed tiles of this K block
+                    umma_commit(&empty_b[bb.s]);           // and the unpacked weight tile
+                    ld.advance(NL);
+                    bb.advance(NB);
                 }
                 if (!ok) break;
                 umma_commit(&tmem_full[a]);
@@ -225,19 +261,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const GemmParams 
             const int m = mt * GM_BM + lq * 32 + lane;
             const float sxm = (m < p.M) ? p.sx[m] : 0.0f;
             const int xs = (m < p.M) ? p.xsum[m] : 0;
-            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(lq * 32) << 16) + a * GM_BN;
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(lq * 32) << 16) + a * BN;
 #pragma unroll 1
-            for (int c0 = 0; c0 < GM_BN; c0 += 32) {
+            for (int c0 = 0; c0 < BN; c0 += 32) {
                 int v[32];
                 tmem_ld_32x32b_x32(taddr + c0, v);
                 tmem_ld_wait();
-                if (c0 + 32 == GM_BN) {
+                if (c0 + 32 == BN) {
                     // accumulator fully read: hand the TMEM buffer back before the stores
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&tmem_empty[a]);
                 }
-                const int n0 = nt * GM_BN + c0;
+                const int n0 = nt * BN + c0;
                 if (m < p.M && n0 < p.N) {
 #pragma unroll
                     for (int c = 0; c < 32; ++c) v[c] -= xs;      // weights were multiplied as t+1
@@ -296,19 +332,25 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const GemmParams 
         const int utid = threadIdx.x - (2 + GM_EPI_WARPS) * 32;   // 0..255
         const int uwarp = utid >> 5;
         const int g = lane >> 2, t = lane & 3;
-        uint32_t it = 0;
-        for (int tile = blockIdx.x; tile < total_tiles && !*s_abort; tile += gridDim.x) {
+        // Group `grp` unpacks the K blocks whose running index is congruent to grp: the latency
+        // chain of one block (barrier, loads, stores, proxy fence, arrive) overlaps the next block's.
+        const int grp = uwarp / GM_GROUP_WARPS, gwarp = uwarp % GM_GROUP_WARPS;
+        RingPos ld, bb;
+        ld.advance_by(NL, grp);
+        bb.advance_by(NB, grp);
+        uint32_t kcount = grp;                               // running K-block index of this group's next block
+        uint32_t kseen = 0;                                  // running index of the current tile's first block
+        for (int tile = blockIdx.x; tile < total_tiles && !*s_abort; tile += gridDim.x, kseen += k_blocks) {
             bool ok = true;
-            for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-                const int s = it % GM_STAGES;
-                if (!wait_or_abort(&full_load[s], (it / GM_STAGES) & 1, s_abort)) { ok = false; break; }
-                const uint8_t* pk = s_p + s * GM_P_BYTES;
-                uint8_t* bt = s_b + s * GM_B_BYTES;
-                // 16 packed tiles (16-column blocks) per stage, 2 per warp.  Lane (g,t) holds, for
-                // column g + 8h, the 32 consecutive k = 32t .. 32t+31: two 16-byte chunks per column.
+            for (; kcount < kseen + k_blocks; kcount += GM_UNPACK_GROUPS) {
+                // the packed tiles have landed and the MMAs that read this B slot have finished
+                if (!wait_or_abort(&full_load[ld.s], ld.phase, s_abort) || !wait_or_abort(&empty_b[bb.s], bb.phase ^ 1, s_abort)) { ok = false; break; }
+                const uint8_t* pk = s_p + ld.s * P_BYTES;
+                uint8_t* bt = s_b + bb.s * B_BYTES;
+                // P_TILES packed tiles (16-column blocks) per stage, spread over the group's warps.  Lane (g,t)
+                // holds, for column g + 8h, the 32 consecutive k = 32t .. 32t+31: two 16-byte chunks per column.
 #pragma unroll
-                for (int u = 0; u < GM_P_TILES / GM_UNPACK_WARPS; ++u) {
-                    const int tix = uwarp * (GM_P_TILES / GM_UNPACK_WARPS) + u;
+                for (int tix = gwarp; tix < P_TILES; tix += GM_GROUP_WARPS) {
                     const uint4 wv = *reinterpret_cast<const uint4*>(pk + tix * TILE_BYTES + lane * 16);
                     const uint32_t w[4] = {wv.x, wv.y, wv.z, wv.w};     // word q = h | (h2 << 1)
 #pragma unroll
@@ -328,7 +370,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const GemmParams 
                 }
                 fence_proxy_async_smem();   // generic-proxy writes -> visible to the tensor core (async proxy)
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&full_b[s]);
+                if (lane == 0) mbar_arrive(&full_b[bb.s]);
+                ld.advance_by(NL, GM_UNPACK_GROUPS);
+                bb.advance_by(NB, GM_UNPACK_GROUPS);
             }
             if (!ok) break;
         }
@@ -338,7 +382,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const GemmParams 
     __syncthreads();
     if (warp == 2) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, GM_TMEM_COLS);
+        tmem_dealloc(tmem_base, TMEM_COLS);
     }
 }
 
@@ -360,6 +404,26 @@ static EncodeTiledFn get_encode_tiled() {
             fn = reinterpret_cast<EncodeTiledFn>(ptr);
     }
     return fn;
+}
+
+template <int BN>
+static int launch_gemm(const CUtensorMap& map, const GemmParams& p, cudaStream_t st) {
+    const int64_t tiles = ceil_div<int64_t>(p.M, GM_BM) * ceil_div<int64_t>(p.N, BN);
+    const unsigned grid = static_cast<unsigned>(std::min<int64_t>(tiles, sm_count()));
+    auto kern = gemm_tcgen05_kernel<BN>;
+    BT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(gm_smem_bytes<BN>())));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(GM_THREADS);
+    cfg.dynamicSmemBytes = gm_smem_bytes<BN>();
+    cfg.stream = st;
+    cudaLaunchAttribute attrs[1];
+    attrs[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attrs;
+    cfg.numAttrs = 1;
+    BT_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, map, p));
+    return BT_OK;
 }
 
 }  // namespace bt
@@ -401,20 +465,18 @@ extern "C" int bt_gemm_tiled_i8(const int8_t* Xq, const float* sx, const int32_t
     p.NB = static_cast<int>(ceil_div<int64_t>(N, TILE_N));
     p.y_dtype = y_dtype;
 
-    const int64_t tiles = ceil_div<int64_t>(M, GM_BM) * ceil_div<int64_t>(N, GM_BN);
-    const unsigned grid = static_cast<unsigned>(std::min<int64_t>(tiles, sm_count()));
-    BT_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    static_cast<int>(GM_SMEM_BYTES)));
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(grid);
-    cfg.blockDim = dim3(GM_THREADS);
-    cfg.dynamicSmemBytes = GM_SMEM_BYTES;
-    cfg.stream = static_cast<cudaStream_t>(stream);
-    cudaLaunchAttribute attrs[1];
-    attrs[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attrs[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attrs;
-    cfg.numAttrs = 1;
-    BT_CUDA_OK(cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel, map, p));
-    return BT_OK;
+    // the widest output tile that still gives every SM a tile; narrow tiles for small problems
+    const int64_t m_tiles = ceil_div<int64_t>(M, GM_BM);
+    const int sms = sm_count();
+    int bn = 64;
+    if (m_tiles * ceil_div<int64_t>(N, 256) >= sms) bn = 256;
+    else if (m_tiles * ceil_div<int64_t>(N, 128) >= sms) bn = 128;
+    if (const char* e = std::getenv("BITTORCH_B200_GEMM_BN")) {      // testing / tuning override
+        const int v = std::atoi(e);
+        if (v == 64 || v == 128 || v == 256) bn = v;
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (bn == 256) return launch_gemm<256>(map, p, st);
+    if (bn == 128) return launch_gemm<128>(map, p, st);
+    return launch_gemm<64>(map, p, st);
 }

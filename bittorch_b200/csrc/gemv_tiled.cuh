@@ -3,14 +3,14 @@
 // One CTA per SM (grid = min(#SMs, column blocks)), no clusters, no global scratch.  Each
 // CTA owns a contiguous run of 16-column blocks, i.e. one contiguous byte range of the
 // tiled buffer, which a producer lane streams with 1-D TMA bulk copies into an mbarrier
-// ring (8 KB stages, up to 64 KB) — starting BEFORE the programmatic-dependent-launch wait,
+// ring (32 KB stages, up to 96 KB) — starting BEFORE the programmatic-dependent-launch wait,
 // because weights never depend on the preceding kernel, so with back-to-back layers the
 // weight stream of layer i+1 overlaps the tail of layer i.
 //
 // After the wait the CTA (16 consumer warps) quantizes the activation rows itself (FUSED:
 // per-row absmax over all of K, reciprocal scale, roundf, clamp — bit-identical to
 // bt_act_quant_i8) or copies pre-quantized int8 rows, into shared memory.  Then warp w
-// takes tile 16*stage + w: one 16-byte vector per lane, the four 2-bit planes masked in
+// takes four consecutive tiles of every stage: one 16-byte vector per lane and tile, the four 2-bit planes masked in
 // place (bytes (t+1)*4^i for planes 0..2, -t*64 for plane 3), each masked word a dp4a against
 // the matching activation word.  Per tile and activation row: 16 logic ops shared by all rows + 16 dp4a.  When a
 // warp leaves a column block it folds its planes (>> 2i), sums the four k-lanes with
@@ -30,9 +30,10 @@ namespace bt {
 constexpr int GT_CONSUMER_WARPS = 16;
 constexpr int GT_NCONS = GT_CONSUMER_WARPS * 32;
 constexpr int GT_THREADS = GT_NCONS + 32;              // + one producer warp
-constexpr int GT_STAGE_TILES = 16;                     // one tile per consumer warp
-constexpr int GT_STAGE_BYTES = GT_STAGE_TILES * TILE_BYTES;   // 8 KB
-constexpr int GT_MAX_STAGES = 8;                       // up to 64 KB of weights in flight per CTA
+constexpr int GT_TPW = 4;                              // consecutive tiles per consumer warp and stage
+constexpr int GT_STAGE_TILES = GT_CONSUMER_WARPS * GT_TPW;
+constexpr int GT_STAGE_BYTES = GT_STAGE_TILES * TILE_BYTES;   // 32 KB
+constexpr int GT_MAX_STAGES = 3;                       // up to 96 KB of weights in flight per CTA
 constexpr int GT_MAX_ROWS = 8;                         // activation rows per launch (accumulators live in registers)
 constexpr int GT_X_PAD = 16;                           // bytes of padding per activation row in shared memory
 constexpr int GT_SLOT_BUDGET = 32;                     // column blocks per CTA x padded rows, bounds the partial-sum slots
@@ -292,11 +293,14 @@ gemv_tiled_kernel(const GemvTiledParams p) {
             }
         };
 
-        // no divisions in the loop: slot / parity and (column block, k tile) advance incrementally
+        // Warp w takes the GT_TPW consecutive tiles GT_TPW*w .. of every stage.  No divisions in
+        // the loop: slot / parity and (column block, k tile) advance incrementally.
         int s = 0;
         uint32_t parity = 0;
-        int nb_local = 0, kt = warp;                        // tile `warp` of the chunk
+        int nb_local = 0, kt = GT_TPW * warp;
         while (kt >= p.KT) { kt -= p.KT; ++nb_local; }
+        const uint8_t* lane_ring = s_ring + warp * (GT_TPW * TILE_BYTES) + lane * 16;
+        const int8_t* lane_x = s_x + 32 * t;
         for (int it = 0; it < n_iters; ++it) {
             if (!mbar_wait_bounded(&s_full[s], parity)) {
                 report_wait_timeout();
@@ -304,15 +308,9 @@ gemv_tiled_kernel(const GemvTiledParams p) {
                 break;
             }
             if (it == 0) BT_STAMP(10);
-            if (it == 1) BT_STAMP(11);
-            if (it == 2) BT_STAMP(15);
-            if (it == 1) BT_STAMP_WARP(64);
-            if (nb_local < nbl) {                            // this warp has a tile in this stage
-                if (nb_local != cur_nb) {
-                    if (cur_nb >= 0) flush(cur_nb);
-                    cur_nb = nb_local;
-                }
-                const uint4 wv = *reinterpret_cast<const uint4*>(s_ring + s * GT_STAGE_BYTES + warp * TILE_BYTES + lane * 16);
+            const uint8_t* tp = lane_ring + s * GT_STAGE_BYTES;
+            // one tile: mask the planes, dp4a against the lane's 32 activations of every row
+            auto tile = [&](const uint4 wv, const int8_t* xk) {
                 // planes 0..2: bytes (t+1)*4^i, at most 32, valid as signed; plane 3 owns the top
                 // two bits, where {0x00,0x40,0x80} ^ 0x40 = {+64, 0, -64} = -t*64 as signed bytes
                 int wm[4][4];
@@ -325,10 +323,8 @@ gemv_tiled_kernel(const GemvTiledParams p) {
                 wm[3][2] = (wv.z & 0xC0C0C0C0u) ^ 0x40404040u; wm[3][3] = (wv.w & 0xC0C0C0C0u) ^ 0x40404040u;
 #pragma unroll
                 for (int m = 0; m < MR; ++m) {
-                    // 32 consecutive activations: word 2i + (q>>1)
-                    const int8_t* xp = s_x + m * xstride + kt * TILE_K + 32 * t;
-                    const int4 xa = *reinterpret_cast<const int4*>(xp);
-                    const int4 xb = *reinterpret_cast<const int4*>(xp + 16);
+                    const int4 xa = *reinterpret_cast<const int4*>(xk + m * xstride);        // words 2i + (q>>1)
+                    const int4 xb = *reinterpret_cast<const int4*>(xk + m * xstride + 16);
                     const int xw[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
@@ -338,13 +334,38 @@ gemv_tiled_kernel(const GemvTiledParams p) {
                         acc[m][i][1] = __dp4a(wm[i][3], xw[2 * i + 1], acc[m][i][1]);
                     }
                 }
+            };
+            if (nb_local < nbl && kt + GT_TPW <= p.KT) {
+                // fast path: the warp's four tiles belong to one column block — straight-line code
+                if (nb_local != cur_nb) {
+                    if (cur_nb >= 0) flush(cur_nb);
+                    cur_nb = nb_local;
+                }
+                uint4 wv[GT_TPW];
+#pragma unroll
+                for (int u = 0; u < GT_TPW; ++u) wv[u] = *reinterpret_cast<const uint4*>(tp + u * TILE_BYTES);
+                const int8_t* xk = lane_x + kt * TILE_K;
+#pragma unroll
+                for (int u = 0; u < GT_TPW; ++u) tile(wv[u], xk + u * TILE_K);
+                kt += GT_TPW;
+                if (kt == p.KT) { kt = 0; ++nb_local; }
+            } else {
+#pragma unroll 1
+                for (int u = 0; u < GT_TPW; ++u) {
+                    if (nb_local < nbl) {                    // a real tile (the last stage may be short)
+                        if (nb_local != cur_nb) {
+                            if (cur_nb >= 0) flush(cur_nb);
+                            cur_nb = nb_local;
+                        }
+                        tile(*reinterpret_cast<const uint4*>(tp + u * TILE_BYTES), lane_x + kt * TILE_K);
+                    }
+                    if (++kt == p.KT) { kt = 0; ++nb_local; }
+                }
             }
-            if (it == 1) BT_STAMP_WARP(80);
             __syncwarp();
             if (lane == 0) mbar_arrive(&s_empty[s]);
-            if (it == 1) BT_STAMP_WARP(96);
             if (++s == stages) { s = 0; parity ^= 1; }
-            kt += GT_STAGE_TILES;
+            kt += GT_STAGE_TILES - GT_TPW;                   // on to this warp's tiles of the next stage
             while (kt >= p.KT) { kt -= p.KT; ++nb_local; }
         }
         BT_STAMP(7);

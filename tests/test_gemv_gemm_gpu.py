@@ -114,6 +114,18 @@ def test_gemm_tcgen05_bit_exact(oracle, m, k, n):
     assert _within_gate(y.numpy(), y_ref)
 
 
+@pytest.mark.parametrize("bn", ["64", "128", "256"])
+def test_gemm_every_tile_width_gives_the_same_bits(oracle, bn, monkeypatch):
+    """The launcher picks the output-tile width from the problem size; force each one."""
+    monkeypatch.setenv("BITTORCH_B200_GEMM_BN", bn)
+    for (m, k, n) in [(300, 1024, 720), (17, 4096, 256), (1, 128, 16), (130, 144, 1000)]:
+        prob = _problem(m, k, n, seed=int(bn) + m)
+        acc_ref, y_ref = _reference(oracle, *prob)
+        y, acc = _run("gemm_tiled_i8", *prob, torch.float32)
+        assert np.array_equal(acc.numpy(), acc_ref)
+        assert np.array_equal(y.numpy().view(np.uint32), y_ref.view(np.uint32))
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_gemm_half_outputs(oracle, dtype):
     prob = _problem(200, 384, 328, seed=5)
