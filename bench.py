@@ -487,7 +487,8 @@ def main() -> None:
     dev = torch.device("cuda", local_rank)
     group = None
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        import datetime
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=120))
         group = dist.group.WORLD
     peaks = load_peaks()
 
@@ -566,10 +567,17 @@ def main() -> None:
         line["sweep"] = rows
         line["int8_mm_proxy_tops"] = proxy
     if rank == 0:
-        print(json.dumps(line))
+        print(json.dumps(line), flush=True)
     if world > 1:
+        # Tearing the NCCL communicator down while CUDA graphs that captured its collectives are
+        # still alive blocks forever, so: drop the graph, synchronise, and leave without the
+        # (optional) destroy_process_group.
+        torch.cuda.synchronize()
         dist.barrier()
-        dist.destroy_process_group()
+        graph.reset()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 if __name__ == "__main__":
