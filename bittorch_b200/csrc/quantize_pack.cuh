@@ -1,10 +1,10 @@
 // Fused weight ternarizer + 2-bit packer, and the stand-alone packer / unpacker.
 //
-// One CTA owns 32 consecutive output rows (n) of the master weight.  Pass 1 streams
+// One CTA owns 16 consecutive output rows (n) of the master weight.  Pass 1 streams
 // the rows from HBM to find each row's absmax; pass 2 re-reads the same rows (now in
-// L2: 32 rows are far smaller than the CTA's share of the 126 MB L2 for the shapes of
-// interest), ternarizes, packs four k per byte and transposes 32x32-byte tiles through
-// shared memory so that the [ceil(K/4), N] buffer is written in 32-byte runs along n.
+// L2: 16 rows are far smaller than the CTA's share of the 126 MB L2 for the shapes of
+// interest), ternarizes, packs four k per byte and transposes 128x16-byte tiles through
+// shared memory so that the [ceil(K/4), N] buffer is written in 16-byte runs along n.
 // Algorithmic traffic: sizeof(T) bytes read + 1/4 byte written per weight.
 #pragma once
 
@@ -12,9 +12,9 @@
 
 namespace bt {
 
-constexpr int QP_ROWS = 32;      // output rows per CTA
-constexpr int QP_THREADS = 512;  // 16 warps, 2 rows each
-constexpr int QP_KB_TILE = 32;   // packed bytes (along k) per transposed tile
+constexpr int QP_ROWS = 16;      // output rows per CTA: keeps the rows of all resident CTAs inside L2 for pass 2
+constexpr int QP_THREADS = 512;  // 16 warps, 1 row each
+constexpr int QP_KB_TILE = 128;  // packed bytes (along k) per transposed tile: 4 loads in flight per lane and row
 
 // bittorch/quant/ternary.py:137-142 — sign where |w| > thr, else 0.
 __device__ __forceinline__ int ternary_code(float w, float thr) {
@@ -41,25 +41,30 @@ quantize_pack_kernel(const T* __restrict__ W, int64_t N, int64_t K, int64_t ldw,
         const int64_t n = n0 + r;
         if (n >= N) { if (lane == 0) s_thr[r] = 0.0f; continue; }
         const T* row = W + n * ldw;
-        float m = 0.0f;
-        int nan_seen = 0;
-        for (int64_t kb = lane; kb < KB; kb += 32) {
-            float v[4];
-            const int64_t k = kb * 4;
-            const int valid = (K - k >= 4) ? 4 : static_cast<int>(K - k);
-            load4<T>(row + k, vec_in, valid, v);
+        // max over the bit patterns of |w|: for non-negative floats unsigned order is numeric
+        // order, and every NaN pattern sorts above +inf, so a NaN propagates like torch.max
+        uint32_t mbits = 0;
+        for (int64_t kb0 = lane; kb0 < KB; kb0 += 32 * 8) {
+            float v[8][4];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const float a = fabsf(v[i]);
-                nan_seen |= (a != a);
-                m = fmaxf(m, a);
+            for (int u = 0; u < 8; ++u) {                 // eight independent loads in flight per lane
+                const int64_t kb = kb0 + 32 * u;
+                const int64_t k = kb * 4;
+                const int valid = (kb < KB) ? ((K - k >= 4) ? 4 : static_cast<int>(K - k)) : 0;
+                if (valid > 0) load4<T>(row + k, vec_in, valid, v[u]);
+                else v[u][0] = v[u][1] = v[u][2] = v[u][3] = 0.0f;
             }
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) mbits = max(mbits, __float_as_uint(v[u][i]) & 0x7fffffffu);
         }
-        m = warp_max(m);
-        nan_seen = warp_or(nan_seen);
-        // clamp(min=1e-8) in the storage type; torch.max propagates NaN.
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mbits = max(mbits, __shfl_xor_sync(0xffffffffu, mbits, o));
+        const float m = __uint_as_float(mbits);
+        // clamp(min=1e-8) in the storage type (NaN stays NaN)
         const float floor_ = round_through<T>(1e-8f);
-        float s = nan_seen ? __int_as_float(0x7fc00000) : fmaxf(m, floor_);
+        const float s = (m != m) ? m : fmaxf(m, floor_);
         if (lane == 0) {
             scale_out[n] = s;
             s_thr[r] = round_through<T>(__fmul_rn(threshold_factor, s));
@@ -72,39 +77,46 @@ quantize_pack_kernel(const T* __restrict__ W, int64_t N, int64_t K, int64_t ldw,
     for (int64_t kb0 = 0; kb0 < KB; kb0 += QP_KB_TILE) {
         for (int r = warp; r < QP_ROWS; r += NWARPS) {
             const int64_t n = n0 + r;
-            const int64_t kb = kb0 + lane;
-            uint32_t byte = 0;
-            if (n < N && kb < KB) {
+            const float thr = s_thr[r];
+            float v[QP_KB_TILE / 32][4];
+            int valid[QP_KB_TILE / 32];
+#pragma unroll
+            for (int u = 0; u < QP_KB_TILE / 32; ++u) {    // independent loads first
+                const int64_t kb = kb0 + lane + 32 * u;
                 const int64_t k = kb * 4;
-                const int valid = (K - k >= 4) ? 4 : static_cast<int>(K - k);
-                float v[4];
-                load4<T>(W + n * ldw + k, vec_in, valid, v);
-                const float thr = s_thr[r];
-                int t[4];
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    t[i] = (i < valid) ? ternary_code(v[i], thr) : 0;
-                    byte |= two_bit(t[i]) << (2 * i);
-                }
-                if (codes_out != nullptr) {
-#pragma unroll
-                    for (int i = 0; i < 4; ++i)
-                        if (i < valid) codes_out[n * K + k + i] = static_cast<int8_t>(t[i]);
-                }
-                if (tern_out != nullptr) {
-#pragma unroll
-                    for (int i = 0; i < 4; ++i)
-                        if (i < valid) tern_out[n * K + k + i] = from_float<T>(static_cast<float>(t[i]));
-                }
+                valid[u] = (n < N && kb < KB) ? ((K - k >= 4) ? 4 : static_cast<int>(K - k)) : 0;
+                if (valid[u] > 0) load4<T>(W + n * ldw + k, vec_in, valid[u], v[u]);
             }
-            s_tile[lane][r] = static_cast<uint8_t>(byte);
+#pragma unroll
+            for (int u = 0; u < QP_KB_TILE / 32; ++u) {
+                const int64_t k = (kb0 + lane + 32 * u) * 4;
+                uint32_t byte = 0;
+                if (valid[u] > 0) {
+                    // |w| > thr ? sign(w) : 0 as two compares: code bit 0 = (w > thr), bit 1 = (w < -thr)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        if (i < valid[u])
+                            byte |= ((v[u][i] > thr ? 1u : 0u) | (v[u][i] < -thr ? 2u : 0u)) << (2 * i);
+                    if (codes_out != nullptr || tern_out != nullptr) {
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            if (i >= valid[u]) continue;
+                            const uint32_t c = (byte >> (2 * i)) & 3u;
+                            const int t = static_cast<int>(c & 1u) - static_cast<int>(c >> 1);
+                            if (codes_out != nullptr) codes_out[n * K + k + i] = static_cast<int8_t>(t);
+                            if (tern_out != nullptr) tern_out[n * K + k + i] = from_float<T>(static_cast<float>(t));
+                        }
+                    }
+                }
+                s_tile[lane + 32 * u][r] = static_cast<uint8_t>(byte);
+            }
         }
         __syncthreads();
         if (packed_T != nullptr) {
-            // 32 (kb) x 32 (n) bytes; 256 threads store 4 bytes each along n.
-            if (threadIdx.x < QP_KB_TILE * (QP_ROWS / 4)) {
-                const int kbl = threadIdx.x / (QP_ROWS / 4);
-                const int nl = (threadIdx.x % (QP_ROWS / 4)) * 4;
+            // QP_KB_TILE (kb) x 32 (n) bytes, 4-byte stores along n
+            for (int idx = threadIdx.x; idx < QP_KB_TILE * (QP_ROWS / 4); idx += QP_THREADS) {
+                const int kbl = idx / (QP_ROWS / 4);
+                const int nl = (idx % (QP_ROWS / 4)) * 4;
                 const int64_t kb = kb0 + kbl;
                 const int64_t n = n0 + nl;
                 if (kb < KB && n < N) {
@@ -124,14 +136,16 @@ quantize_pack_kernel(const T* __restrict__ W, int64_t N, int64_t K, int64_t ldw,
 }
 
 // Packs int8 codes [N,K] into the public [ceil(K/4), N] buffer (same tiling as above).
+constexpr int PC_KB_TILE = 32;   // packed bytes (along k) per transposed tile of the stand-alone packer
+
 __global__ void __launch_bounds__(QP_THREADS)
 pack_codes_kernel(const int8_t* __restrict__ codes, int64_t N, int64_t K, uint8_t* __restrict__ packed_T) {
-    __shared__ uint8_t s_tile[QP_KB_TILE][QP_ROWS + 4];
+    __shared__ uint8_t s_tile[PC_KB_TILE][QP_ROWS + 4];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t n0 = static_cast<int64_t>(blockIdx.x) * QP_ROWS;
     const int64_t KB = (K + 3) / 4;
     constexpr int NWARPS = QP_THREADS / 32;
-    for (int64_t kb0 = 0; kb0 < KB; kb0 += QP_KB_TILE) {
+    for (int64_t kb0 = 0; kb0 < KB; kb0 += PC_KB_TILE) {
         for (int r = warp; r < QP_ROWS; r += NWARPS) {
             const int64_t n = n0 + r, kb = kb0 + lane;
             uint32_t byte = 0;
@@ -145,7 +159,7 @@ pack_codes_kernel(const int8_t* __restrict__ codes, int64_t N, int64_t K, uint8_
             s_tile[lane][r] = static_cast<uint8_t>(byte);
         }
         __syncthreads();
-        for (int idx = threadIdx.x; idx < QP_KB_TILE * QP_ROWS; idx += QP_THREADS) {
+        for (int idx = threadIdx.x; idx < PC_KB_TILE * QP_ROWS; idx += QP_THREADS) {
             const int kbl = idx / QP_ROWS, nl = idx % QP_ROWS;
             const int64_t kb = kb0 + kbl, n = n0 + nl;
             if (kb < KB && n < N) packed_T[kb * N + n] = s_tile[kbl][nl];
