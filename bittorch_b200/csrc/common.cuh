@@ -221,11 +221,26 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait: gives up after `limit` polls (each poll may itself suspend for a
-// hardware-defined short time).  Returns false on timeout; the caller records it.
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+constexpr unsigned long long WAIT_BUDGET_NS = 2000000000ull;   // a device-side wait gives up after 2 s
+
+// Bounded wait: polls the barrier (each poll may itself suspend for a hardware-defined
+// short time) and gives up after `limit` polls or WAIT_BUDGET_NS of wall time, whichever
+// comes first.  Returns false on timeout; the caller records it.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, uint32_t limit = (1u << 22)) {
-    for (uint32_t i = 0; i < limit; ++i)
+    unsigned long long t0 = 0;
+    for (uint32_t i = 0; i < limit; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 1023u) == 1023u) {
+            const unsigned long long now = global_timer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > WAIT_BUDGET_NS) return false;
+        }
+    }
     return false;
 }
 

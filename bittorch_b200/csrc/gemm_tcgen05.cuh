@@ -137,11 +137,57 @@ template <int BN> __host__ __device__ constexpr uint32_t gm_idesc() {
     return (2u << 4) | (1u << 7) | (0u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(GM_BM >> 4) << 24);
 }
 
+// Stores up to 32 consecutive outputs of one row (16-byte stores when the row segment is
+// complete and aligned).
+__device__ __forceinline__ void store_row32(void* Y, int y_dtype, int64_t base, const float (&y)[32], int valid) {
+    const bool full = valid >= 32;
+    if (y_dtype == BT_F32) {
+        float* out = reinterpret_cast<float*>(Y) + base;
+        if (full && aligned(out, 16)) {
+#pragma unroll
+            for (int c = 0; c < 32; c += 4)
+                *reinterpret_cast<float4*>(out + c) = make_float4(y[c], y[c + 1], y[c + 2], y[c + 3]);
+        } else {
+#pragma unroll
+            for (int c = 0; c < 32; ++c)
+                if (c < valid) out[c] = y[c];
+        }
+    } else {
+        uint16_t* out = reinterpret_cast<uint16_t*>(Y) + base;
+        uint32_t pk[16];
+#pragma unroll
+        for (int c = 0; c < 32; c += 2) {
+            if (y_dtype == BT_F16) {
+                __half2 h = __floats2half2_rn(y[c], y[c + 1]);
+                pk[c / 2] = *reinterpret_cast<uint32_t*>(&h);
+            } else {
+                __nv_bfloat162 h = __floats2bfloat162_rn(y[c], y[c + 1]);
+                pk[c / 2] = *reinterpret_cast<uint32_t*>(&h);
+            }
+        }
+        if (full && aligned(out, 16)) {
+#pragma unroll
+            for (int c = 0; c < 16; c += 4)
+                *reinterpret_cast<uint4*>(out + 2 * c) = make_uint4(pk[c], pk[c + 1], pk[c + 2], pk[c + 3]);
+        } else {
+#pragma unroll
+            for (int c = 0; c < 32; ++c)
+                if (c < valid) out[c] = static_cast<uint16_t>(pk[c / 2] >> (16 * (c & 1)));
+        }
+    }
+}
+
 // Bounded mbarrier wait that also gives up when another role has already failed.
 __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    unsigned long long t0 = 0;
     for (uint32_t i = 0; i < (1u << 22); ++i) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 255u) == 255u && *abort_flag) return false;
+        if ((i & 255u) == 255u) {
+            if (*abort_flag) return false;
+            const unsigned long long now = global_timer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > WAIT_BUDGET_NS) break;
+        }
     }
     report_wait_timeout();
     *abort_flag = 1;
@@ -150,7 +196,7 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, vo
 
 template <int BN>
 __global__ void __launch_bounds__(GM_THREADS, 1)
-gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const GemmParams p) {
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, const GemmParams p) {
     constexpr int NL = GemmCfg<BN>::NL, NB = GemmCfg<BN>::NB;
     constexpr int P_TILES = gm_p_tiles<BN>(), P_BYTES = gm_p_bytes<BN>(), B_BYTES = gm_b_bytes<BN>();
     constexpr uint32_t TMEM_COLS = 2 * BN;               // double-buffered accumulator (power of two >= 128)
@@ -207,15 +253,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const GemmParams 
             for (int tile = blockIdx.x; tile < total_tiles && !*s_abort; tile += gridDim.x) {
                 const int mt = tile % m_tiles, nt = tile / m_tiles;
                 const int nb0 = nt * P_TILES;
-                const int nb_valid = min(P_TILES, p.NB - nb0);
                 bool ok = true;
                 for (int kb = 0; kb < k_blocks; ++kb) {
                     if (!wait_or_abort(&empty_load[ld.s], ld.phase ^ 1, s_abort)) { ok = false; break; }
-                    mbar_expect_tx(&full_load[ld.s], GM_A_BYTES + static_cast<uint32_t>(nb_valid) * TILE_BYTES);
+                    // two tensor copies per stage: issuing one bulk copy per 512-byte tile from this single
+                    // thread cost more than the MMAs of the stage.  Column blocks past the end arrive as zeros
+                    // (and count their bytes); their outputs are never stored.
+                    mbar_expect_tx(&full_load[ld.s], GM_A_BYTES + P_BYTES);
                     tma_load_2d(s_a + ld.s * GM_A_BYTES, &map_x, kb * GM_BK, mt * GM_BM, &full_load[ld.s]);
-                    for (int j = 0; j < nb_valid; ++j)      // one 512-byte tile per 16-column block
-                        bulk_g2s(s_p + ld.s * P_BYTES + j * TILE_BYTES,
-                                 p.tiled + (static_cast<int64_t>(nb0 + j) * p.KT + kb) * TILE_BYTES, TILE_BYTES, &full_load[ld.s]);
+                    tma_load_2d(s_p + ld.s * P_BYTES, &map_w, kb * (TILE_BYTES / 4), nb0, &full_load[ld.s]);
                     ld.advance(NL);
                 }
                 if (!ok) break;
@@ -288,42 +334,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const GemmParams 
                         const int n = min(n0 + c, p.N - 1);
                         y[c] = dequant(v[c], sxm, __ldg(p.scale + n), p.bias ? __ldg(p.bias + n) : 0.0f, p.bias != nullptr);
                     }
-                    const int64_t base = static_cast<int64_t>(m) * p.ldy + n0;
-                    const bool full = (n0 + 32 <= p.N);
-                    if (p.y_dtype == BT_F32) {
-                        float* out = reinterpret_cast<float*>(p.Y) + base;
-                        if (full && aligned(out, 16)) {
-#pragma unroll
-                            for (int c = 0; c < 32; c += 4)
-                                *reinterpret_cast<float4*>(out + c) = make_float4(y[c], y[c + 1], y[c + 2], y[c + 3]);
-                        } else {
-#pragma unroll
-                            for (int c = 0; c < 32; ++c)
-                                if (n0 + c < p.N) out[c] = y[c];
-                        }
-                    } else {
-                        uint16_t* out = reinterpret_cast<uint16_t*>(p.Y) + base;
-                        uint32_t pk[16];
-#pragma unroll
-                        for (int c = 0; c < 32; c += 2) {
-                            if (p.y_dtype == BT_F16) {
-                                __half2 h = __floats2half2_rn(y[c], y[c + 1]);
-                                pk[c / 2] = *reinterpret_cast<uint32_t*>(&h);
-                            } else {
-                                __nv_bfloat162 h = __floats2bfloat162_rn(y[c], y[c + 1]);
-                                pk[c / 2] = *reinterpret_cast<uint32_t*>(&h);
-                            }
-                        }
-                        if (full && aligned(out, 16)) {
-#pragma unroll
-                            for (int c = 0; c < 16; c += 4)
-                                *reinterpret_cast<uint4*>(out + 2 * c) = make_uint4(pk[c], pk[c + 1], pk[c + 2], pk[c + 3]);
-                        } else {
-#pragma unroll
-                            for (int c = 0; c < 32; ++c)
-                                if (n0 + c < p.N) out[c] = static_cast<uint16_t>(pk[c / 2] >> (16 * (c & 1)));
-                        }
-                    }
+                    store_row32(p.Y, p.y_dtype, static_cast<int64_t>(m) * p.ldy + n0, y, min(32, p.N - n0));
                 }
             }
         }
@@ -406,8 +417,27 @@ static EncodeTiledFn get_encode_tiled() {
     return fn;
 }
 
+// Tensor map over the tiled weights seen as [column blocks][KT * 128 words]: one box is the `block_rows`
+// 512-byte tiles that one K block of an output tile needs.
+static int encode_weight_map(EncodeTiledFn encode, const GemmParams& p, int block_rows, CUtensorMap* map) {
+    const cuuint64_t gdim[2] = {static_cast<cuuint64_t>(p.KT) * (TILE_BYTES / 4), static_cast<cuuint64_t>(p.NB)};
+    const cuuint64_t gstride[1] = {static_cast<cuuint64_t>(p.KT) * TILE_BYTES};
+    const cuuint32_t box[2] = {TILE_BYTES / 4, static_cast<cuuint32_t>(block_rows)};
+    const cuuint32_t estride[2] = {1, 1};
+    const CUresult cr = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<uint8_t*>(p.tiled), gdim, gstride, box, estride,
+                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (cr != CUDA_SUCCESS) {
+        set_error("bt_gemm_tiled_i8: cuTensorMapEncodeTiled (weights) failed with code %d", static_cast<int>(cr));
+        return BT_ERR_CUDA;
+    }
+    return BT_OK;
+}
+
 template <int BN>
-static int launch_gemm(const CUtensorMap& map, const GemmParams& p, cudaStream_t st) {
+static int launch_gemm(EncodeTiledFn encode, const CUtensorMap& map, const GemmParams& p, cudaStream_t st) {
+    CUtensorMap map_w;
+    if (const int rc = encode_weight_map(encode, p, gm_p_tiles<BN>(), &map_w)) return rc;
     const int64_t tiles = ceil_div<int64_t>(p.M, GM_BM) * ceil_div<int64_t>(p.N, BN);
     const unsigned grid = static_cast<unsigned>(std::min<int64_t>(tiles, sm_count()));
     auto kern = gemm_tcgen05_kernel<BN>;
@@ -422,9 +452,11 @@ static int launch_gemm(const CUtensorMap& map, const GemmParams& p, cudaStream_t
     attrs[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attrs;
     cfg.numAttrs = 1;
-    BT_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, map, p));
+    BT_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, map, map_w, p));
     return BT_OK;
 }
+
+static int launch_gemm_pair(EncodeTiledFn encode, const CUtensorMap& map, const GemmParams& p, cudaStream_t st);   // gemm_tcgen05_2cta.cuh
 
 }  // namespace bt
 
@@ -476,7 +508,11 @@ extern "C" int bt_gemm_tiled_i8(const int8_t* Xq, const float* sx, const int32_t
         if (v == 64 || v == 128 || v == 256) bn = v;
     }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (bn == 256) return launch_gemm<256>(map, p, st);
-    if (bn == 128) return launch_gemm<128>(map, p, st);
-    return launch_gemm<64>(map, p, st);
+    // CTA pairs (cta_group::2, 256 x 256 tiles) once there are enough 256-row tiles to fill the GPU
+    bool pair = M > GM_BM && ceil_div<int64_t>(M, 256) * ceil_div<int64_t>(N, 256) >= (sms / 2) * 7 / 10;
+    if (const char* e = std::getenv("BITTORCH_B200_GEMM_PAIR")) pair = std::atoi(e) != 0;      // testing / tuning override
+    if (pair) return launch_gemm_pair(encode, map, p, st);
+    if (bn == 256) return launch_gemm<256>(encode, map, p, st);
+    if (bn == 128) return launch_gemm<128>(encode, map, p, st);
+    return launch_gemm<64>(encode, map, p, st);
 }

@@ -34,6 +34,7 @@ int sm_count() {
 
 #include "act_quant.cuh"
 #include "gemm_tcgen05.cuh"
+#include "gemm_tcgen05_2cta.cuh"
 #include "gemv.cuh"
 #include "gemv_tiled.cuh"
 #include "linear_float.cuh"

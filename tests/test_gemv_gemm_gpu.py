@@ -126,6 +126,18 @@ def test_gemm_every_tile_width_gives_the_same_bits(oracle, bn, monkeypatch):
         assert np.array_equal(y.numpy().view(np.uint32), y_ref.view(np.uint32))
 
 
+@pytest.mark.parametrize("m,k,n", [(256, 128, 256), (300, 1024, 720), (129, 4096, 256), (1000, 2560, 6912),
+                                   (512, 144, 1000), (2, 128, 16), (2048, 1024, 1024)])
+def test_gemm_cta_pair_kernel_bit_exact(oracle, m, k, n, monkeypatch):
+    """The cta_group::2 kernel (two CTAs share a 256 x 256 tile), forced for every shape."""
+    monkeypatch.setenv("BITTORCH_B200_GEMM_PAIR", "1")
+    prob = _problem(m, k, n, seed=m + 2 * k + 3 * n)
+    acc_ref, y_ref = _reference(oracle, *prob)
+    y, acc = _run("gemm_tiled_i8", *prob, torch.float32)
+    assert np.array_equal(acc.numpy(), acc_ref)
+    assert np.array_equal(y.numpy().view(np.uint32), y_ref.view(np.uint32))
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_gemm_half_outputs(oracle, dtype):
     prob = _problem(200, 384, 328, seed=5)
