@@ -270,26 +270,40 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     } else if (warp == 1) {
         // ================= MMA issuer =================
         if (lane == 0) {
+            // The issuing thread has a budget of roughly one MMA (about 128 cycles) between bursts before the
+            // tensor pipe runs dry, and a barrier wait costs about that much even when it succeeds at once.  So
+            // the barriers of the NEXT K block are polled in the middle of this block's burst, where the poll's
+            // latency hides behind the queued MMAs; the blocking wait runs only when that poll failed.
             RingPos ld, bb;
             uint32_t tcount = 0;
+            bool ready = false;
             for (int tile = blockIdx.x; tile < total_tiles && !*s_abort; tile += gridDim.x, ++tcount) {
                 const uint32_t a = tcount & 1;
                 if (!wait_or_abort(&tmem_empty[a], ((tcount >> 1) & 1) ^ 1, s_abort)) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + a * BN;
+                const bool last_tile = tile + static_cast<int>(gridDim.x) >= total_tiles;
                 bool ok = true;
                 for (int kb = 0; kb < k_blocks; ++kb) {
-                    if (!wait_or_abort(&full_load[ld.s], ld.phase, s_abort) || !wait_or_abort(&full_b[bb.s], bb.phase, s_abort)) { ok = false; break; }
+                    if (!ready && (!wait_or_abort(&full_load[ld.s], ld.phase, s_abort) || !wait_or_abort(&full_b[bb.s], bb.phase, s_abort))) { ok = false; break; }
                     tc_fence_after();
                     const uint64_t da = umma_desc_sw128(smem_u32(s_a + ld.s * GM_A_BYTES));
                     const uint64_t db = umma_desc_sw128(smem_u32(s_b + bb.s * B_BYTES));
+                    RingPos ld_next = ld, bb_next = bb;
+                    ld_next.advance(NL);
+                    bb_next.advance(NB);
+                    const bool more = kb + 1 < k_blocks || !last_tile;
+                    ready = false;
 #pragma unroll
-                    for (int k = 0; k < GM_BK / 32; ++k)   // +32 bytes along K = +2 in the (>>4) address field
+                    for (int k = 0; k < GM_BK / 32; ++k) {   // +32 bytes along K = +2 in the (>>4) address field
                         umma_i8(d_tmem, da + 2 * k, db + 2 * k, gm_idesc<BN>(), (kb > 0 || k > 0) ? 1u : 0u);
+                        if (k == 1 && more)
+                            ready = mbar_test_wait(&full_load[ld_next.s], ld_next.phase) & mbar_test_wait(&full_b[bb_next.s], bb_next.phase);
+                    }
                     umma_commit(&empty_load[ld.s]);        // frees the activation + packed tiles of this K block
                     umma_commit(&empty_b[bb.s]);           // and the unpacked weight tile
-                    ld.advance(NL);
-                    bb.advance(NB);
+                    ld = ld_next;
+                    bb = bb_next;
                 }
                 if (!ok) break;
                 umma_commit(&tmem_full[a]);

@@ -86,6 +86,10 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
     uint32_t* s_tmem = reinterpret_cast<uint32_t*>(tmem_empty + 2);
     __shared__ int s_abort_storage;
     volatile int* s_abort = &s_abort_storage;
+#ifdef BT_TRACE
+    __shared__ long long s_issue_time[G2_NL];
+    volatile long long* issue_time = s_issue_time;
+#endif
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();             // 0 = leader, 1 = peer
@@ -144,6 +148,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
                     if (!wait_or_abort(&empty_load[ld.s], ld.phase ^ 1, s_abort)) { ok = false; break; }
 #ifdef BT_TRACE
                     t_w += clock64() - p0; n_w += 1;
+                    issue_time[ld.s] = clock64();
 #endif
                     if (leader) mbar_expect_tx(&full_a[ld.s], 2 * GM_A_BYTES);
                     tma_load_2d_pair(s_a + ld.s * GM_A_BYTES, &map_x, kb * GM_BK, mt * 256 + static_cast<int>(rank) * GM_BM,
@@ -161,58 +166,41 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
     } else if (warp == 1) {
         // ================= MMA issuer (leader CTA only) =================
         if (leader && lane == 0) {
+            // next K block's barriers are polled inside this block's MMA burst (see the one-CTA kernel)
             RingPos ld, bb;
             uint32_t tcount = 0;
-#ifdef BT_TRACE
-            long long t_a = 0, t_b = 0, t_e = 0, t_i = 0, n_k = 0;
-            const long long t_start = clock64();
-#endif
+            bool ready = false;
             for (int tile = pair; tile < total_tiles && !*s_abort; tile += n_pairs, ++tcount) {
                 const uint32_t a = tcount & 1;
-#ifdef BT_TRACE
-                const long long e0 = clock64();
-#endif
                 if (!wait_or_abort(&tmem_empty[a], ((tcount >> 1) & 1) ^ 1, s_abort)) break;
-#ifdef BT_TRACE
-                t_e += clock64() - e0;
-#endif
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + a * G2_BN;
+                const bool last_tile = tile + n_pairs >= total_tiles;
                 bool ok = true;
                 for (int kb = 0; kb < k_blocks; ++kb) {
-#ifdef BT_TRACE
-                    const long long c0 = clock64();
-                    if (!wait_or_abort(&full_a[ld.s], ld.phase, s_abort)) { ok = false; break; }
-                    const long long c1 = clock64();
-                    if (!wait_or_abort(&full_b[bb.s], bb.phase, s_abort)) { ok = false; break; }
-                    const long long c2 = clock64();
-                    t_a += c1 - c0; t_b += c2 - c1; n_k += 1;
-#else
-                    if (!wait_or_abort(&full_a[ld.s], ld.phase, s_abort) || !wait_or_abort(&full_b[bb.s], bb.phase, s_abort)) { ok = false; break; }
-#endif
+                    if (!ready && (!wait_or_abort(&full_a[ld.s], ld.phase, s_abort) || !wait_or_abort(&full_b[bb.s], bb.phase, s_abort))) { ok = false; break; }
                     tc_fence_after();
                     const uint64_t da = umma_desc_sw128(smem_u32(s_a + ld.s * GM_A_BYTES));
                     const uint64_t db = umma_desc_sw128(smem_u32(s_b + bb.s * G2_B_BYTES));
+                    RingPos ld_next = ld, bb_next = bb;
+                    ld_next.advance(NL);
+                    bb_next.advance(NB);
+                    const bool more = kb + 1 < k_blocks || !last_tile;
+                    ready = false;
 #pragma unroll
-                    for (int k = 0; k < GM_BK / 32; ++k)
+                    for (int k = 0; k < GM_BK / 32; ++k) {
                         umma_i8_pair(d_tmem, da + 2 * k, db + 2 * k, G2_IDESC, (kb > 0 || k > 0) ? 1u : 0u);
+                        if (k == 1 && more)
+                            ready = mbar_test_wait(&full_a[ld_next.s], ld_next.phase) & mbar_test_wait(&full_b[bb_next.s], bb_next.phase);
+                    }
                     umma_commit_pair(&empty_load[ld.s]);
                     umma_commit_pair(&empty_b[bb.s]);
-#ifdef BT_TRACE
-                    t_i += clock64() - c2;
-#endif
-                    ld.advance(NL);
-                    bb.advance(NB);
+                    ld = ld_next;
+                    bb = bb_next;
                 }
                 if (!ok) break;
                 umma_commit_pair(&tmem_full[a]);
             }
-#ifdef BT_TRACE
-            if (blockIdx.x == 0) {
-                g_trace[100] += t_a; g_trace[101] += t_b; g_trace[102] += n_k; g_trace[103] += t_e; g_trace[104] += tcount;
-                g_trace[111] += t_i; g_trace[112] += clock64() - t_start;
-            }
-#endif
         }
     } else if (warp < 2 + GM_EPI_WARPS) {
         // ================= epilogue (both CTAs, own 128 rows) =================
@@ -267,7 +255,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
         bb.advance_by(NB, grp);
         uint32_t kcount = grp, kseen = 0;
 #ifdef BT_TRACE
-        long long t_p = 0, t_eb = 0, t_u = 0, n_u = 0, t_f = 0, t_ar = 0;
+        long long t_p = 0, t_eb = 0, t_u = 0, n_u = 0, t_f = 0, t_ar = 0, t_lat_p = 0, n_lat_p = 0;
 #endif
         for (int tile = pair; tile < total_tiles && !*s_abort; tile += n_pairs, kseen += k_blocks) {
             bool ok = true;
@@ -279,6 +267,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
                 if (!wait_or_abort(&empty_b[bb.s], bb.phase ^ 1, s_abort)) { ok = false; break; }
                 const long long u2 = clock64();
                 t_p += u1 - u0; t_eb += u2 - u1; n_u += 1;
+                if (u1 - u0 > 60) { t_lat_p += u1 - issue_time[ld.s]; n_lat_p += 1; }
 #else
                 if (!wait_or_abort(&full_p[ld.s], ld.phase, s_abort) || !wait_or_abort(&empty_b[bb.s], bb.phase ^ 1, s_abort)) { ok = false; break; }
 #endif
@@ -322,7 +311,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
             if (!ok) break;
         }
 #ifdef BT_TRACE
-        if (blockIdx.x == 0 && utid == 0) { g_trace[105] += t_p; g_trace[106] += t_eb; g_trace[107] += n_u; g_trace[108] += t_u; g_trace[113] += t_f; g_trace[114] += t_ar; }
+        if (blockIdx.x == 0 && utid == 0) { g_trace[105] += t_p; g_trace[106] += t_eb; g_trace[107] += n_u; g_trace[108] += t_u; g_trace[113] += t_f; g_trace[114] += t_ar; g_trace[117] += t_lat_p; g_trace[118] += n_lat_p; }
 #endif
     }
 
