@@ -70,6 +70,7 @@ __device__ __forceinline__ void report_wait_timeout() { atomicExch(&g_device_sta
 // first CTA's first thread receives the global nanosecond timer.  Compiled out otherwise.
 #ifdef BT_TRACE
 __device__ unsigned long long g_trace[128];
+__device__ int g_knob;   // bring-up experiments: bit flags that switch parts of a kernel off (results are then wrong)
 __device__ __forceinline__ void bt_stamp(int i) {
     if (blockIdx.x == 0 && blockIdx.y == 0 && (threadIdx.x & 31) == 0) {
         unsigned long long t;

@@ -37,8 +37,9 @@ constexpr int GM_THREADS = (2 + GM_EPI_WARPS + GM_UNPACK_WARPS) * 32;          /
 // TMA) is deep because its latency is a global-memory round trip, the ring of unpacked
 // weight tiles is shallow because it is filled from shared memory.
 template <int BN> struct GemmCfg;
-template <> struct GemmCfg<256> { static constexpr int NL = 5, NB = 3; };
-template <> struct GemmCfg<128> { static constexpr int NL = 6, NB = 4; };
+// Powers of two: the MMA issuer derives slot and phase from one block counter with masks and shifts.
+template <> struct GemmCfg<256> { static constexpr int NL = 4, NB = 4; };
+template <> struct GemmCfg<128> { static constexpr int NL = 8, NB = 4; };
 template <> struct GemmCfg<64> { static constexpr int NL = 8, NB = 4; };
 
 template <int BN> __host__ __device__ constexpr int gm_p_tiles() { return BN / TILE_N; }                 // packed tiles per stage
@@ -106,6 +107,53 @@ __device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t a_desc, uint64
 // Arrives on the mbarrier once every MMA issued so far by this thread has completed.
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// One K block (128 inputs = four K=32 MMAs) issued as a single instruction sequence:
+//   MMA, MMA, poll(next block's two "full" barriers), MMA, MMA, commit(c0), commit(c1)
+// and only then the two poll predicates are read.  The issuing thread has about one MMA time (128 cycles) of
+// slack between bursts; with one asm statement per instruction (a setp per MMA, a selp right behind every poll) the
+// bookkeeping of a K block alone cost 200-300 cycles and the tensor pipe ran at 60 % of its rate.
+// Returns non-zero when both polled barriers had already completed their phase.
+// PAIR: cta_group::2 MMAs, commits multicast to both CTAs of the pair.
+template <bool PAIR>
+__device__ __forceinline__ uint32_t umma_i8_burst4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                   uint32_t accumulate_first, uint64_t* poll0, uint32_t parity0, uint64_t* poll1,
+                                                   uint32_t parity1, uint64_t* commit0, uint64_t* commit1) {
+    uint32_t ok0, ok1;
+#define BT_MMA1_AT(off) "add.s64 ta, %3, " #off ";\n\tadd.s64 tb, %4, " #off ";\n\ttcgen05.mma.cta_group::1.kind::i8 [%2], ta, tb, %5, pt;\n\t"
+#define BT_MMA2_AT(off) "add.s64 ta, %3, " #off ";\n\tadd.s64 tb, %4, " #off ";\n\ttcgen05.mma.cta_group::2.kind::i8 [%2], ta, tb, %5, pt;\n\t"
+#define BT_POLLS "mbarrier.test_wait.parity.shared::cta.b64 p0, [%7], %8;\n\tmbarrier.test_wait.parity.shared::cta.b64 p1, [%9], %10;\n\t"
+    if (PAIR) {
+        asm volatile(
+            "{\n\t.reg .pred pa, pt, p0, p1;\n\t.reg .b64 ta, tb;\n\t"
+            "setp.ne.b32 pa, %6, 0;\n\tsetp.eq.b32 pt, 0, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::i8 [%2], %3, %4, %5, pa;\n\t"
+            BT_MMA2_AT(2) BT_POLLS BT_MMA2_AT(4) BT_MMA2_AT(6)
+            "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%11], %13;\n\t"
+            "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%12], %13;\n\t"
+            "selp.u32 %0, 1, 0, p0;\n\tselp.u32 %1, 1, 0, p1;\n\t}"
+            : "=r"(ok0), "=r"(ok1)
+            : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate_first), "r"(smem_u32(poll0)), "r"(parity0),
+              "r"(smem_u32(poll1)), "r"(parity1), "r"(smem_u32(commit0)), "r"(smem_u32(commit1)), "h"(static_cast<uint16_t>(3))
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred pa, pt, p0, p1;\n\t.reg .b64 ta, tb;\n\t"
+            "setp.ne.b32 pa, %6, 0;\n\tsetp.eq.b32 pt, 0, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::i8 [%2], %3, %4, %5, pa;\n\t"
+            BT_MMA1_AT(2) BT_POLLS BT_MMA1_AT(4) BT_MMA1_AT(6)
+            "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%11];\n\t"
+            "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%12];\n\t"
+            "selp.u32 %0, 1, 0, p0;\n\tselp.u32 %1, 1, 0, p1;\n\t}"
+            : "=r"(ok0), "=r"(ok1)
+            : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate_first), "r"(smem_u32(poll0)), "r"(parity0),
+              "r"(smem_u32(poll1)), "r"(parity1), "r"(smem_u32(commit0)), "r"(smem_u32(commit1))
+            : "memory");
+    }
+#undef BT_MMA1_AT
+#undef BT_MMA2_AT
+#undef BT_POLLS
+    return ok0 & ok1;
 }
 __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, int (&v)[32]) {
     asm volatile(
@@ -270,40 +318,30 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     } else if (warp == 1) {
         // ================= MMA issuer =================
         if (lane == 0) {
-            // The issuing thread has a budget of roughly one MMA (about 128 cycles) between bursts before the
-            // tensor pipe runs dry, and a barrier wait costs about that much even when it succeeds at once.  So
-            // the barriers of the NEXT K block are polled in the middle of this block's burst, where the poll's
-            // latency hides behind the queued MMAs; the blocking wait runs only when that poll failed.
-            RingPos ld, bb;
-            uint32_t tcount = 0;
+            // The barriers of the NEXT K block are polled inside this block's MMA burst (umma_i8_burst4), where the
+            // poll's latency hides behind the queued MMAs; the blocking wait runs only when that poll failed.
+            // Everything this thread does between two bursts delays the next one, so slot and phase of both rings
+            // come from one block counter with masks and shifts (ring depths are powers of two).
+            static_assert((NL & (NL - 1)) == 0 && (NB & (NB - 1)) == 0, "ring depths must be powers of two");
+            static_assert(GM_BK == 128, "umma_i8_burst4 issues four K=32 MMAs");
+            const uint64_t desc_a0 = umma_desc_sw128(smem_u32(s_a)), desc_b0 = umma_desc_sw128(smem_u32(s_b));
+            uint32_t cnt = 0, tcount = 0;      // K blocks / tiles issued so far
             bool ready = false;
             for (int tile = blockIdx.x; tile < total_tiles && !*s_abort; tile += gridDim.x, ++tcount) {
                 const uint32_t a = tcount & 1;
                 if (!wait_or_abort(&tmem_empty[a], ((tcount >> 1) & 1) ^ 1, s_abort)) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + a * BN;
-                const bool last_tile = tile + static_cast<int>(gridDim.x) >= total_tiles;
                 bool ok = true;
                 for (int kb = 0; kb < k_blocks; ++kb) {
-                    if (!ready && (!wait_or_abort(&full_load[ld.s], ld.phase, s_abort) || !wait_or_abort(&full_b[bb.s], bb.phase, s_abort))) { ok = false; break; }
+                    const uint32_t sl = cnt & (NL - 1), sb = cnt & (NB - 1), nx = cnt + 1, nsl = nx & (NL - 1), nsb = nx & (NB - 1);
+                    if (!ready && (!wait_or_abort(&full_load[sl], (cnt / NL) & 1, s_abort) || !wait_or_abort(&full_b[sb], (cnt / NB) & 1, s_abort))) { ok = false; break; }
                     tc_fence_after();
-                    const uint64_t da = umma_desc_sw128(smem_u32(s_a + ld.s * GM_A_BYTES));
-                    const uint64_t db = umma_desc_sw128(smem_u32(s_b + bb.s * B_BYTES));
-                    RingPos ld_next = ld, bb_next = bb;
-                    ld_next.advance(NL);
-                    bb_next.advance(NB);
-                    const bool more = kb + 1 < k_blocks || !last_tile;
-                    ready = false;
-#pragma unroll
-                    for (int k = 0; k < GM_BK / 32; ++k) {   // +32 bytes along K = +2 in the (>>4) address field
-                        umma_i8(d_tmem, da + 2 * k, db + 2 * k, gm_idesc<BN>(), (kb > 0 || k > 0) ? 1u : 0u);
-                        if (k == 1 && more)
-                            ready = mbar_test_wait(&full_load[ld_next.s], ld_next.phase) & mbar_test_wait(&full_b[bb_next.s], bb_next.phase);
-                    }
-                    umma_commit(&empty_load[ld.s]);        // frees the activation + packed tiles of this K block
-                    umma_commit(&empty_b[bb.s]);           // and the unpacked weight tile
-                    ld = ld_next;
-                    bb = bb_next;
+                    // the commits free the activation + packed tiles of this K block and its unpacked weight tile
+                    ready = umma_i8_burst4<false>(d_tmem, desc_a0 + sl * (GM_A_BYTES >> 4), desc_b0 + sb * (B_BYTES >> 4), gm_idesc<BN>(),
+                                                  kb > 0 ? 1u : 0u, &full_load[nsl], (nx / NL) & 1, &full_b[nsb], (nx / NB) & 1,
+                                                  &empty_load[sl], &empty_b[sb]) != 0;
+                    cnt = nx;
                 }
                 if (!ok) break;
                 umma_commit(&tmem_full[a]);

@@ -24,7 +24,7 @@ namespace bt {
 
 constexpr int G2_BN = 256;                      // columns of the pair's tile
 constexpr int G2_HALF = G2_BN / 2;              // columns unpacked by each CTA
-constexpr int G2_NL = 6, G2_NB = 4;
+constexpr int G2_NL = 8, G2_NB = 4;       // powers of two (see the MMA issuer)
 constexpr int G2_P_TILES = G2_HALF / TILE_N;    // 8 packed tiles per CTA and K block
 constexpr int G2_P_BYTES = G2_P_TILES * TILE_BYTES;      // 4 KB
 constexpr int G2_B_BYTES = G2_HALF * GM_BK;              // 16 KB
@@ -129,6 +129,9 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
     const uint32_t tmem_base = *s_tmem;
     pdl_launch_dependents();
     pdl_wait();
+#ifdef BT_TRACE
+    const int knob = g_knob;
+#endif
 
     if (warp == 0) {
         // ================= producer (both CTAs) =================
@@ -150,11 +153,25 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
                     t_w += clock64() - p0; n_w += 1;
                     issue_time[ld.s] = clock64();
 #endif
+#ifdef BT_TRACE
+                    if ((knob & 2) && n_w > NL) {
+                        if (leader) mbar_arrive(&full_a[ld.s]);
+                    } else
+#endif
+                    {
                     if (leader) mbar_expect_tx(&full_a[ld.s], 2 * GM_A_BYTES);
                     tma_load_2d_pair(s_a + ld.s * GM_A_BYTES, &map_x, kb * GM_BK, mt * 256 + static_cast<int>(rank) * GM_BM,
                                      smem_u32(&full_a[ld.s]) & G2_PEER_BIT_MASK);
+                    }
+#ifdef BT_TRACE
+                    if ((knob & 8) && n_w > NL) {
+                        mbar_arrive(&full_p[ld.s]);
+                    } else
+#endif
+                    {
                     mbar_expect_tx(&full_p[ld.s], G2_P_BYTES);      // column blocks past the end arrive as zeros
                     tma_load_2d(s_p + ld.s * G2_P_BYTES, &map_w, kb * (TILE_BYTES / 4), nb0, &full_p[ld.s]);
+                    }
                     ld.advance(NL);
                 }
                 if (!ok) break;
@@ -167,40 +184,38 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
         // ================= MMA issuer (leader CTA only) =================
         if (leader && lane == 0) {
             // next K block's barriers are polled inside this block's MMA burst (see the one-CTA kernel)
-            RingPos ld, bb;
-            uint32_t tcount = 0;
+            static_assert((NL & (NL - 1)) == 0 && (NB & (NB - 1)) == 0, "ring depths must be powers of two");
+            const uint64_t desc_a0 = umma_desc_sw128(smem_u32(s_a)), desc_b0 = umma_desc_sw128(smem_u32(s_b));
+            uint32_t cnt = 0, tcount = 0;      // K blocks / tiles issued so far
             bool ready = false;
+#ifdef BT_TRACE
+            long long n_block = 0;
+            const long long t_start = clock64();
+#endif
             for (int tile = pair; tile < total_tiles && !*s_abort; tile += n_pairs, ++tcount) {
                 const uint32_t a = tcount & 1;
                 if (!wait_or_abort(&tmem_empty[a], ((tcount >> 1) & 1) ^ 1, s_abort)) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + a * G2_BN;
-                const bool last_tile = tile + n_pairs >= total_tiles;
                 bool ok = true;
                 for (int kb = 0; kb < k_blocks; ++kb) {
-                    if (!ready && (!wait_or_abort(&full_a[ld.s], ld.phase, s_abort) || !wait_or_abort(&full_b[bb.s], bb.phase, s_abort))) { ok = false; break; }
+                    const uint32_t sl = cnt & (NL - 1), sb = cnt & (NB - 1), nx = cnt + 1, nsl = nx & (NL - 1), nsb = nx & (NB - 1);
+#ifdef BT_TRACE
+                    n_block += ready ? 0 : 1;
+#endif
+                    if (!ready && (!wait_or_abort(&full_a[sl], (cnt / NL) & 1, s_abort) || !wait_or_abort(&full_b[sb], (cnt / NB) & 1, s_abort))) { ok = false; break; }
                     tc_fence_after();
-                    const uint64_t da = umma_desc_sw128(smem_u32(s_a + ld.s * GM_A_BYTES));
-                    const uint64_t db = umma_desc_sw128(smem_u32(s_b + bb.s * G2_B_BYTES));
-                    RingPos ld_next = ld, bb_next = bb;
-                    ld_next.advance(NL);
-                    bb_next.advance(NB);
-                    const bool more = kb + 1 < k_blocks || !last_tile;
-                    ready = false;
-#pragma unroll
-                    for (int k = 0; k < GM_BK / 32; ++k) {
-                        umma_i8_pair(d_tmem, da + 2 * k, db + 2 * k, G2_IDESC, (kb > 0 || k > 0) ? 1u : 0u);
-                        if (k == 1 && more)
-                            ready = mbar_test_wait(&full_a[ld_next.s], ld_next.phase) & mbar_test_wait(&full_b[bb_next.s], bb_next.phase);
-                    }
-                    umma_commit_pair(&empty_load[ld.s]);
-                    umma_commit_pair(&empty_b[bb.s]);
-                    ld = ld_next;
-                    bb = bb_next;
+                    ready = umma_i8_burst4<true>(d_tmem, desc_a0 + sl * (GM_A_BYTES >> 4), desc_b0 + sb * (G2_B_BYTES >> 4), G2_IDESC,
+                                                 kb > 0 ? 1u : 0u, &full_a[nsl], (nx / NL) & 1, &full_b[nsb], (nx / NB) & 1,
+                                                 &empty_load[sl], &empty_b[sb]) != 0;
+                    cnt = nx;
                 }
                 if (!ok) break;
                 umma_commit_pair(&tmem_full[a]);
             }
+#ifdef BT_TRACE
+            if (blockIdx.x == 0) { g_trace[102] += cnt; g_trace[104] += tcount; g_trace[111] += n_block; g_trace[112] += clock64() - t_start; }
+#endif
         }
     } else if (warp < 2 + GM_EPI_WARPS) {
         // ================= epilogue (both CTAs, own 128 rows) =================
@@ -226,6 +241,9 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
                     if (lane == 0) mbar_arrive_remote(map_to_rank(&tmem_empty[a], 0));
                 }
                 const int n0 = nt * G2_BN + c0;
+#ifdef BT_TRACE
+                if (knob & 4) continue;
+#endif
                 if (m < p.M && n0 < p.N) {
 #pragma unroll
                     for (int c = 0; c < 32; ++c) v[c] -= xs;
@@ -273,6 +291,9 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
 #endif
                 const uint8_t* pk = s_p + ld.s * G2_P_BYTES;
                 uint8_t* bt = s_b + bb.s * G2_B_BYTES;
+#ifdef BT_TRACE
+                if (!(knob & 1))
+#endif
 #pragma unroll
                 for (int tix = gwarp; tix < G2_P_TILES; tix += GM_GROUP_WARPS) {
                     const uint4 wv = *reinterpret_cast<const uint4*>(pk + tix * TILE_BYTES + lane * 16);
