@@ -242,6 +242,16 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, vo
     return false;
 }
 
+// The same wait run by all 32 lanes of a converged warp, with a warp-uniform result.
+__device__ __forceinline__ bool wait_or_abort_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    return __all_sync(0xffffffffu, wait_or_abort(bar, parity, abort_flag));
+}
+__device__ __forceinline__ bool elect_one_lane() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+    return pred != 0;
+}
+
 template <int BN>
 __global__ void __launch_bounds__(GM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, const GemmParams p) {
@@ -317,34 +327,40 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         }
     } else if (warp == 1) {
         // ================= MMA issuer =================
-        if (lane == 0) {
-            // The barriers of the NEXT K block are polled inside this block's MMA burst (umma_i8_burst4), where the
-            // poll's latency hides behind the queued MMAs; the blocking wait runs only when that poll failed.
-            // Everything this thread does between two bursts delays the next one, so slot and phase of both rings
-            // come from one block counter with masks and shifts (ring depths are powers of two).
+        // The whole warp runs the loop and one elected lane issues.  With warp-uniform control flow the compiler keeps
+        // the block counter, descriptors and barrier addresses in uniform registers, which is what the tcgen05
+        // instructions take; computed by a single diverged lane they had to be moved there for every K block, and
+        // everything this warp does between two bursts delays the next one (the slack is about one MMA, 128 cycles).
+        // For the same reason slot and phase of both rings come from one block counter with masks and shifts.
+        {
             static_assert((NL & (NL - 1)) == 0 && (NB & (NB - 1)) == 0, "ring depths must be powers of two");
             static_assert(GM_BK == 128, "umma_i8_burst4 issues four K=32 MMAs");
             const uint64_t desc_a0 = umma_desc_sw128(smem_u32(s_a)), desc_b0 = umma_desc_sw128(smem_u32(s_b));
+            const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);   // the same value, provably warp-uniform
             uint32_t cnt = 0, tcount = 0;      // K blocks / tiles issued so far
             bool ready = false;
-            for (int tile = blockIdx.x; tile < total_tiles && !*s_abort; tile += gridDim.x, ++tcount) {
+            for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++tcount) {
+                if (__any_sync(0xffffffffu, *s_abort != 0)) break;
                 const uint32_t a = tcount & 1;
-                if (!wait_or_abort(&tmem_empty[a], ((tcount >> 1) & 1) ^ 1, s_abort)) break;
+                if (!wait_or_abort_warp(&tmem_empty[a], ((tcount >> 1) & 1) ^ 1, s_abort)) break;
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + a * BN;
+                const uint32_t d_tmem = tmem_u + a * BN;
                 bool ok = true;
                 for (int kb = 0; kb < k_blocks; ++kb) {
                     const uint32_t sl = cnt & (NL - 1), sb = cnt & (NB - 1), nx = cnt + 1, nsl = nx & (NL - 1), nsb = nx & (NB - 1);
-                    if (!ready && (!wait_or_abort(&full_load[sl], (cnt / NL) & 1, s_abort) || !wait_or_abort(&full_b[sb], (cnt / NB) & 1, s_abort))) { ok = false; break; }
+                    if (!ready && (!wait_or_abort_warp(&full_load[sl], (cnt / NL) & 1, s_abort) || !wait_or_abort_warp(&full_b[sb], (cnt / NB) & 1, s_abort))) { ok = false; break; }
                     tc_fence_after();
-                    // the commits free the activation + packed tiles of this K block and its unpacked weight tile
-                    ready = umma_i8_burst4<false>(d_tmem, desc_a0 + sl * (GM_A_BYTES >> 4), desc_b0 + sb * (B_BYTES >> 4), gm_idesc<BN>(),
-                                                  kb > 0 ? 1u : 0u, &full_load[nsl], (nx / NL) & 1, &full_b[nsb], (nx / NB) & 1,
-                                                  &empty_load[sl], &empty_b[sb]) != 0;
+                    uint32_t polled = 0;
+                    if (elect_one_lane())   // the commits free the activation + packed tiles of this K block and its unpacked weight tile
+                        polled = umma_i8_burst4<false>(d_tmem, desc_a0 + sl * (GM_A_BYTES >> 4), desc_b0 + sb * (B_BYTES >> 4), gm_idesc<BN>(),
+                                                       kb > 0 ? 1u : 0u, &full_load[nsl], (nx / NL) & 1, &full_b[nsb], (nx / NB) & 1,
+                                                       &empty_load[sl], &empty_b[sb]);
+                    ready = __any_sync(0xffffffffu, polled != 0);
                     cnt = nx;
                 }
                 if (!ok) break;
-                umma_commit(&tmem_full[a]);
+                if (elect_one_lane()) umma_commit(&tmem_full[a]);
+                __syncwarp();
             }
         }
     } else if (warp < 2 + GM_EPI_WARPS) {

@@ -182,39 +182,45 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
         }
     } else if (warp == 1) {
         // ================= MMA issuer (leader CTA only) =================
-        if (leader && lane == 0) {
-            // next K block's barriers are polled inside this block's MMA burst (see the one-CTA kernel)
+        // warp-uniform loop, one elected lane issues (see the one-CTA kernel)
+        if (leader) {
             static_assert((NL & (NL - 1)) == 0 && (NB & (NB - 1)) == 0, "ring depths must be powers of two");
             const uint64_t desc_a0 = umma_desc_sw128(smem_u32(s_a)), desc_b0 = umma_desc_sw128(smem_u32(s_b));
+            const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);   // the same value, provably warp-uniform
             uint32_t cnt = 0, tcount = 0;      // K blocks / tiles issued so far
             bool ready = false;
 #ifdef BT_TRACE
             long long n_block = 0;
             const long long t_start = clock64();
 #endif
-            for (int tile = pair; tile < total_tiles && !*s_abort; tile += n_pairs, ++tcount) {
+            for (int tile = pair; tile < total_tiles; tile += n_pairs, ++tcount) {
+                if (__any_sync(0xffffffffu, *s_abort != 0)) break;
                 const uint32_t a = tcount & 1;
-                if (!wait_or_abort(&tmem_empty[a], ((tcount >> 1) & 1) ^ 1, s_abort)) break;
+                if (!wait_or_abort_warp(&tmem_empty[a], ((tcount >> 1) & 1) ^ 1, s_abort)) break;
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + a * G2_BN;
+                const uint32_t d_tmem = tmem_u + a * G2_BN;
                 bool ok = true;
                 for (int kb = 0; kb < k_blocks; ++kb) {
                     const uint32_t sl = cnt & (NL - 1), sb = cnt & (NB - 1), nx = cnt + 1, nsl = nx & (NL - 1), nsb = nx & (NB - 1);
 #ifdef BT_TRACE
                     n_block += ready ? 0 : 1;
 #endif
-                    if (!ready && (!wait_or_abort(&full_a[sl], (cnt / NL) & 1, s_abort) || !wait_or_abort(&full_b[sb], (cnt / NB) & 1, s_abort))) { ok = false; break; }
+                    if (!ready && (!wait_or_abort_warp(&full_a[sl], (cnt / NL) & 1, s_abort) || !wait_or_abort_warp(&full_b[sb], (cnt / NB) & 1, s_abort))) { ok = false; break; }
                     tc_fence_after();
-                    ready = umma_i8_burst4<true>(d_tmem, desc_a0 + sl * (GM_A_BYTES >> 4), desc_b0 + sb * (G2_B_BYTES >> 4), G2_IDESC,
-                                                 kb > 0 ? 1u : 0u, &full_a[nsl], (nx / NL) & 1, &full_b[nsb], (nx / NB) & 1,
-                                                 &empty_load[sl], &empty_b[sb]) != 0;
+                    uint32_t polled = 0;
+                    if (elect_one_lane())
+                        polled = umma_i8_burst4<true>(d_tmem, desc_a0 + sl * (GM_A_BYTES >> 4), desc_b0 + sb * (G2_B_BYTES >> 4), G2_IDESC,
+                                                      kb > 0 ? 1u : 0u, &full_a[nsl], (nx / NL) & 1, &full_b[nsb], (nx / NB) & 1,
+                                                      &empty_load[sl], &empty_b[sb]);
+                    ready = __any_sync(0xffffffffu, polled != 0);
                     cnt = nx;
                 }
                 if (!ok) break;
-                umma_commit_pair(&tmem_full[a]);
+                if (elect_one_lane()) umma_commit_pair(&tmem_full[a]);
+                __syncwarp();
             }
 #ifdef BT_TRACE
-            if (blockIdx.x == 0) { g_trace[102] += cnt; g_trace[104] += tcount; g_trace[111] += n_block; g_trace[112] += clock64() - t_start; }
+            if (blockIdx.x == 0 && lane == 0) { g_trace[102] += cnt; g_trace[104] += tcount; g_trace[111] += n_block; g_trace[112] += clock64() - t_start; }
 #endif
         }
     } else if (warp < 2 + GM_EPI_WARPS) {
@@ -233,8 +239,13 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
 #pragma unroll 1
             for (int c0 = 0; c0 < G2_BN; c0 += 32) {
                 int v[32];
+#ifdef BT_TRACE
+                if (!(knob & 32))
+#endif
+                {
                 tmem_ld_32x32b_x32(taddr + c0, v);
                 tmem_ld_wait();
+                }
                 if (c0 + 32 == G2_BN) {
                     tc_fence_before();
                     __syncwarp();
