@@ -70,7 +70,6 @@ __device__ __forceinline__ void report_wait_timeout() { atomicExch(&g_device_sta
 // first CTA's first thread receives the global nanosecond timer.  Compiled out otherwise.
 #ifdef BT_TRACE
 __device__ unsigned long long g_trace[128];
-__device__ int g_knob;   // bring-up experiments: bit flags that switch parts of a kernel off (results are then wrong)
 __device__ __forceinline__ void bt_stamp(int i) {
     if (blockIdx.x == 0 && blockIdx.y == 0 && (threadIdx.x & 31) == 0) {
         unsigned long long t;
@@ -216,18 +215,6 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// Non-blocking poll (test_wait never suspends the thread).
-__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
         : "r"(smem_u32(bar)), "r"(parity)

@@ -36,18 +36,22 @@ constexpr int GM_THREADS = (2 + GM_EPI_WARPS + GM_UNPACK_WARPS) * 32;          /
 // Per output-tile width BN: the load ring (activation tile + 2-bit weight tiles, filled by
 // TMA) is deep because its latency is a global-memory round trip, the ring of unpacked
 // weight tiles is shallow because it is filled from shared memory.
-template <int BN> struct GemmCfg;
 // Powers of two: the MMA issuer derives slot and phase from one block counter with masks and shifts.
+// NL is the depth of the load ring when the activation tile has all 128 rows; with fewer rows
+// (M <= 120) only those rows are copied and the ring gets deeper (gemm_ring_depth).
+template <int BN> struct GemmCfg;
 template <> struct GemmCfg<256> { static constexpr int NL = 4, NB = 4; };
 template <> struct GemmCfg<128> { static constexpr int NL = 8, NB = 4; };
 template <> struct GemmCfg<64> { static constexpr int NL = 8, NB = 4; };
+constexpr int GM_MAX_NL = 32;
+constexpr size_t GM_SMEM_LIMIT = 227 * 1024;
 
 template <int BN> __host__ __device__ constexpr int gm_p_tiles() { return BN / TILE_N; }                 // packed tiles per stage
 template <int BN> __host__ __device__ constexpr int gm_p_bytes() { return gm_p_tiles<BN>() * TILE_BYTES; }
 template <int BN> __host__ __device__ constexpr int gm_b_bytes() { return BN * GM_BK; }
-template <int BN> constexpr size_t gm_smem_bytes() {
-    return 1024 /*alignment slack*/ + static_cast<size_t>(GemmCfg<BN>::NL) * (GM_A_BYTES + gm_p_bytes<BN>()) +
-           static_cast<size_t>(GemmCfg<BN>::NB) * gm_b_bytes<BN>() + 512;
+template <int BN> constexpr size_t gm_smem_bytes(int nl, int a_rows) {
+    return 1024 /*alignment slack*/ + static_cast<size_t>(nl) * (static_cast<size_t>(a_rows) * GM_BK + gm_p_bytes<BN>()) +
+           static_cast<size_t>(GemmCfg<BN>::NB) * gm_b_bytes<BN>() + 1024 /*barriers*/;
 }
 
 // Position in a ring of mbarrier-guarded stages (no divisions in the loops).
@@ -75,6 +79,8 @@ struct GemmParams {
     int KT;        // 128-wide k tiles in the tiled layout
     int NB;        // 16-column blocks in the tiled layout
     int y_dtype;
+    int a_rows;    // rows of the activation tile that are copied (a multiple of 8; 128 unless M is small)
+    int nl_log2;   // log2 of the load ring's depth
 };
 
 // ---- tcgen05 / TMA PTX wrappers ----------------------------------------------------------
@@ -242,6 +248,14 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, vo
     return false;
 }
 
+__device__ __forceinline__ uint32_t map_to_cta(const void* local_smem_ptr, uint32_t cta_rank) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(local_smem_ptr)), "r"(cta_rank));
+    return remote;
+}
+__device__ __forceinline__ void st_cluster_v4(uint32_t cluster_addr, int a, int b, int c, int d) {
+    asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(cluster_addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
 // The same wait run by all 32 lanes of a converged warp, with a warp-uniform result.
 __device__ __forceinline__ bool wait_or_abort_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
     return __all_sync(0xffffffffu, wait_or_abort(bar, parity, abort_flag));
@@ -252,16 +266,26 @@ __device__ __forceinline__ bool elect_one_lane() {
     return pred != 0;
 }
 
-template <int BN>
+// SPLIT (M <= 32 rows): one output tile per thread-block cluster, CTA r of the cluster contracts the r-th slice of
+// K, and the partial accumulators meet in distributed shared memory: CTA r finishes BN / cluster-size columns of the
+// tile, so every CTA sends each owner its rows x columns block, adds what it received and stores.  The issue of a
+// tcgen05.mma costs about as much as a 128 x 256 x 32 MMA runs, whatever its width, so a narrow batch is spread
+// over the SMs by splitting K under full-width tiles, not by narrowing the tiles.
+template <int BN, bool SPLIT>
 __global__ void __launch_bounds__(GM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, const GemmParams p) {
-    constexpr int NL = GemmCfg<BN>::NL, NB = GemmCfg<BN>::NB;
+    constexpr int NB = GemmCfg<BN>::NB;
+    // With few activation rows only those rows are copied per K block and the ring's stages are that much closer
+    // together (and there are more of them).  The MMA still reads 128 rows from a stage's base: the rows past
+    // a_rows are whatever follows in shared memory, and the accumulator rows they produce are never stored.
+    const int NL = 1 << p.nl_log2;
+    const int a_stride = p.a_rows * GM_BK;
     constexpr int P_TILES = gm_p_tiles<BN>(), P_BYTES = gm_p_bytes<BN>(), B_BYTES = gm_b_bytes<BN>();
     constexpr uint32_t TMEM_COLS = 2 * BN;               // double-buffered accumulator (power of two >= 128)
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* s_a = smem;                                 // [NL] activation tiles, 128-byte swizzle
-    uint8_t* s_b = s_a + NL * GM_A_BYTES;                // [NB] unpacked weight tiles, 128-byte swizzle
+    uint8_t* s_b = s_a + NL * a_stride;                  // [NB] unpacked weight tiles, 128-byte swizzle
     uint8_t* s_p = s_b + NB * B_BYTES;                   // [NL] packed 2-bit tiles
     uint64_t* bars = reinterpret_cast<uint64_t*>(s_p + NL * P_BYTES);
     uint64_t* full_load = bars;                          // [NL] producer -> unpack, MMA
@@ -271,6 +295,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     uint64_t* tmem_full = empty_b + NB;                  // [2] MMA -> epilogue
     uint64_t* tmem_empty = tmem_full + 2;                // [2] epilogue -> MMA
     uint32_t* s_tmem = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+    int* s_stage = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(bars) + 1024);   // SPLIT: [cluster size][a_rows][BN / cluster size]
     __shared__ int s_abort_storage;
     volatile int* s_abort = &s_abort_storage;
 
@@ -278,7 +303,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     const int m_tiles = (p.M + GM_BM - 1) / GM_BM;
     const int n_tiles = (p.N + BN - 1) / BN;
     const int total_tiles = m_tiles * n_tiles;
-    const int k_blocks = (p.K + GM_BK - 1) / GM_BK;
+    const int k_blocks_all = (p.K + GM_BK - 1) / GM_BK;
+    // SPLIT: this CTA's tile and K slice; otherwise a persistent loop over tiles and all of K
+    const int csize = SPLIT ? static_cast<int>(cluster_nctarank()) : 1;
+    const int crank = SPLIT ? static_cast<int>(cluster_ctarank()) : 0;
+    const int kb_lo = SPLIT ? crank * k_blocks_all / csize : 0;
+    const int k_blocks = SPLIT ? (crank + 1) * k_blocks_all / csize - kb_lo : k_blocks_all;
+    const int tile_first = SPLIT ? static_cast<int>(blockIdx.x) / csize : static_cast<int>(blockIdx.x);
+    const int tile_step = SPLIT ? total_tiles : static_cast<int>(gridDim.x);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < NL; ++s) {
@@ -301,6 +333,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *s_tmem;
+    if (SPLIT) cluster_sync_all();   // every CTA of the cluster has started: its shared memory may be written
     pdl_launch_dependents();
     pdl_wait();   // activations (and their scales) come from the preceding kernel
 
@@ -308,7 +341,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         // ================= producer =================
         if (lane == 0) {
             RingPos ld;
-            for (int tile = blockIdx.x; tile < total_tiles && !*s_abort; tile += gridDim.x) {
+            for (int tile = tile_first; tile < total_tiles && !*s_abort; tile += tile_step) {
                 const int mt = tile % m_tiles, nt = tile / m_tiles;
                 const int nb0 = nt * P_TILES;
                 bool ok = true;
@@ -317,9 +350,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                     // two tensor copies per stage: issuing one bulk copy per 512-byte tile from this single
                     // thread cost more than the MMAs of the stage.  Column blocks past the end arrive as zeros
                     // (and count their bytes); their outputs are never stored.
-                    mbar_expect_tx(&full_load[ld.s], GM_A_BYTES + P_BYTES);
-                    tma_load_2d(s_a + ld.s * GM_A_BYTES, &map_x, kb * GM_BK, mt * GM_BM, &full_load[ld.s]);
-                    tma_load_2d(s_p + ld.s * P_BYTES, &map_w, kb * (TILE_BYTES / 4), nb0, &full_load[ld.s]);
+                    mbar_expect_tx(&full_load[ld.s], a_stride + P_BYTES);
+                    tma_load_2d(s_a + ld.s * a_stride, &map_x, (kb_lo + kb) * GM_BK, mt * GM_BM, &full_load[ld.s]);
+                    tma_load_2d(s_p + ld.s * P_BYTES, &map_w, (kb_lo + kb) * (TILE_BYTES / 4), nb0, &full_load[ld.s]);
                     ld.advance(NL);
                 }
                 if (!ok) break;
@@ -333,13 +366,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         // everything this warp does between two bursts delays the next one (the slack is about one MMA, 128 cycles).
         // For the same reason slot and phase of both rings come from one block counter with masks and shifts.
         {
-            static_assert((NL & (NL - 1)) == 0 && (NB & (NB - 1)) == 0, "ring depths must be powers of two");
+            static_assert((NB & (NB - 1)) == 0, "ring depths must be powers of two");
             static_assert(GM_BK == 128, "umma_i8_burst4 issues four K=32 MMAs");
             const uint64_t desc_a0 = umma_desc_sw128(smem_u32(s_a)), desc_b0 = umma_desc_sw128(smem_u32(s_b));
             const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);   // the same value, provably warp-uniform
+            const uint32_t nl_mask = NL - 1, nl_log2 = p.nl_log2, a_step = a_stride >> 4;
             uint32_t cnt = 0, tcount = 0;      // K blocks / tiles issued so far
             bool ready = false;
-            for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++tcount) {
+            for (int tile = tile_first; tile < total_tiles; tile += tile_step, ++tcount) {
                 if (__any_sync(0xffffffffu, *s_abort != 0)) break;
                 const uint32_t a = tcount & 1;
                 if (!wait_or_abort_warp(&tmem_empty[a], ((tcount >> 1) & 1) ^ 1, s_abort)) break;
@@ -347,13 +381,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                 const uint32_t d_tmem = tmem_u + a * BN;
                 bool ok = true;
                 for (int kb = 0; kb < k_blocks; ++kb) {
-                    const uint32_t sl = cnt & (NL - 1), sb = cnt & (NB - 1), nx = cnt + 1, nsl = nx & (NL - 1), nsb = nx & (NB - 1);
-                    if (!ready && (!wait_or_abort_warp(&full_load[sl], (cnt / NL) & 1, s_abort) || !wait_or_abort_warp(&full_b[sb], (cnt / NB) & 1, s_abort))) { ok = false; break; }
+                    const uint32_t sl = cnt & nl_mask, sb = cnt & (NB - 1), nx = cnt + 1, nsl = nx & nl_mask, nsb = nx & (NB - 1);
+                    if (!ready && (!wait_or_abort_warp(&full_load[sl], (cnt >> nl_log2) & 1, s_abort) || !wait_or_abort_warp(&full_b[sb], (cnt / NB) & 1, s_abort))) { ok = false; break; }
                     tc_fence_after();
                     uint32_t polled = 0;
                     if (elect_one_lane())   // the commits free the activation + packed tiles of this K block and its unpacked weight tile
-                        polled = umma_i8_burst4<false>(d_tmem, desc_a0 + sl * (GM_A_BYTES >> 4), desc_b0 + sb * (B_BYTES >> 4), gm_idesc<BN>(),
-                                                       kb > 0 ? 1u : 0u, &full_load[nsl], (nx / NL) & 1, &full_b[nsb], (nx / NB) & 1,
+                        polled = umma_i8_burst4<false>(d_tmem, desc_a0 + sl * a_step, desc_b0 + sb * (B_BYTES >> 4), gm_idesc<BN>(),
+                                                       kb > 0 ? 1u : 0u, &full_load[nsl], (nx >> nl_log2) & 1, &full_b[nsb], (nx / NB) & 1,
                                                        &empty_load[sl], &empty_b[sb]);
                     ready = __any_sync(0xffffffffu, polled != 0);
                     cnt = nx;
@@ -367,7 +401,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         // ================= epilogue =================
         const int lq = warp & 3;                       // TMEM lane quarter this warp may access
         uint32_t tcount = 0;
-        for (int tile = blockIdx.x; tile < total_tiles && !*s_abort; tile += gridDim.x, ++tcount) {
+        for (int tile = tile_first; tile < total_tiles && !*s_abort; tile += tile_step, ++tcount) {
             const int mt = tile % m_tiles, nt = tile / m_tiles;
             const uint32_t a = tcount & 1;
             if (!wait_or_abort(&tmem_full[a], (tcount >> 1) & 1, s_abort)) break;
@@ -376,8 +410,32 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             const float sxm = (m < p.M) ? p.sx[m] : 0.0f;
             const int xs = (m < p.M) ? p.xsum[m] : 0;
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(lq * 32) << 16) + a * BN;
+            if (SPLIT) {
+                // rows of this lane quarter that exist: send each 32-column chunk to the CTA that finishes it
+                const int cols_own = BN / csize;
+                const int row = lq * 32 + lane;
+                if (lq * 32 < p.a_rows) {
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
+                    for (int c0 = 0; c0 < BN; c0 += 32) {
+                        int v[32];
+                        if (k_blocks > 0) {
+                            tmem_ld_32x32b_x32(taddr + c0, v);
+                            tmem_ld_wait();
+                        } else {
+#pragma unroll
+                            for (int c = 0; c < 32; ++c) v[c] = 0;
+                        }
+                        if (row < p.a_rows) {
+                            const uint32_t dst = map_to_cta(&s_stage[(crank * p.a_rows + row) * cols_own + (c0 % cols_own)], static_cast<uint32_t>(c0 / cols_own));
+#pragma unroll
+                            for (int c = 0; c < 32; c += 4) st_cluster_v4(dst + c * 4, v[c], v[c + 1], v[c + 2], v[c + 3]);
+                        }
+                    }
+                }
+                tc_fence_before();
+            }
+#pragma unroll 1
+            for (int c0 = 0; !SPLIT && c0 < BN; c0 += 32) {
                 int v[32];
                 tmem_ld_32x32b_x32(taddr + c0, v);
                 tmem_ld_wait();
@@ -419,7 +477,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         bb.advance_by(NB, grp);
         uint32_t kcount = grp;                               // running K-block index of this group's next block
         uint32_t kseen = 0;                                  // running index of the current tile's first block
-        for (int tile = blockIdx.x; tile < total_tiles && !*s_abort; tile += gridDim.x, kseen += k_blocks) {
+        for (int tile = tile_first; tile < total_tiles && !*s_abort; tile += tile_step, kseen += k_blocks) {
             bool ok = true;
             for (; kcount < kseen + k_blocks; kcount += GM_UNPACK_GROUPS) {
                 // the packed tiles have landed and the MMAs that read this B slot have finished
@@ -459,6 +517,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
 
     tc_fence_before();
     __syncthreads();
+    if (SPLIT) {
+        cluster_sync_all();   // the partial accumulators of this CTA's columns have arrived from every K slice
+        const int cols_own = BN / csize;
+        const int nt = tile_first;                       // one M tile: the tile index is the column tile
+        for (int idx = threadIdx.x; idx < p.M * cols_own; idx += GM_THREADS) {
+            const int c = idx % cols_own, m = idx / cols_own;
+            const int n = nt * BN + crank * cols_own + c;
+            if (n < p.N && !*s_abort) {
+                int acc = -p.xsum[m];                    // weights were multiplied as t+1
+                for (int r = 0; r < csize; ++r) acc += s_stage[(r * p.a_rows + m) * cols_own + c];
+                if (p.acc_out != nullptr) p.acc_out[static_cast<int64_t>(m) * p.N + n] = acc;
+                const float y = dequant(acc, p.sx[m], __ldg(p.scale + n), p.bias ? __ldg(p.bias + n) : 0.0f, p.bias != nullptr);
+                store_out_dt(p.Y, p.y_dtype, static_cast<int64_t>(m) * p.ldy + n, y);
+            }
+        }
+    }
     if (warp == 2) {
         tc_fence_after();
         tmem_dealloc(tmem_base, TMEM_COLS);
@@ -502,26 +576,79 @@ static int encode_weight_map(EncodeTiledFn encode, const GemmParams& p, int bloc
     return BT_OK;
 }
 
+// Depth of the load ring for an activation tile of a_rows rows: the configured depth for full tiles, otherwise
+// the largest power of two (at most GM_MAX_NL, and no more than the K blocks there are) that fits shared memory.
 template <int BN>
-static int launch_gemm(EncodeTiledFn encode, const CUtensorMap& map, const GemmParams& p, cudaStream_t st) {
+static int gemm_ring_depth_log2(int a_rows, int k_blocks, size_t extra_bytes = 0) {
+    int lg = 0;
+    while ((1 << lg) < GemmCfg<BN>::NL) ++lg;
+    if (a_rows == GM_BM) return lg;
+    while ((1 << (lg + 1)) <= GM_MAX_NL && (1 << lg) < k_blocks &&
+           gm_smem_bytes<BN>(1 << (lg + 1), a_rows) + extra_bytes + 1024 <= GM_SMEM_LIMIT)
+        ++lg;
+    return lg;
+}
+
+// Clusters of `split` CTAs of the split-K kernel that can be resident at once (they need `split` free SMs inside one
+// GPC each, so this is less than SMs / split); 0 on error.  Cached per cluster size for the largest footprint.
+static int gemm_split_max_clusters(int split);
+
+// split > 1: one tile per cluster of `split` CTAs, K divided among them (BN = 256, M <= 32)
+template <int BN, bool SPLIT>
+static int launch_gemm(EncodeTiledFn encode, const CUtensorMap& map, GemmParams p, cudaStream_t st, int split = 1) {
     CUtensorMap map_w;
     if (const int rc = encode_weight_map(encode, p, gm_p_tiles<BN>(), &map_w)) return rc;
+    const int k_blocks = static_cast<int>(ceil_div<int64_t>(p.K, GM_BK));
+    const size_t stage_bytes = SPLIT ? static_cast<size_t>(p.a_rows) * BN * 4 : 0;     // received partial accumulators
+    p.nl_log2 = gemm_ring_depth_log2<BN>(p.a_rows, ceil_div(k_blocks, split), stage_bytes);
+    const size_t smem = gm_smem_bytes<BN>(1 << p.nl_log2, p.a_rows) + stage_bytes;
     const int64_t tiles = ceil_div<int64_t>(p.M, GM_BM) * ceil_div<int64_t>(p.N, BN);
-    const unsigned grid = static_cast<unsigned>(std::min<int64_t>(tiles, sm_count()));
-    auto kern = gemm_tcgen05_kernel<BN>;
-    BT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(gm_smem_bytes<BN>())));
+    const unsigned grid = SPLIT ? static_cast<unsigned>(tiles * split) : static_cast<unsigned>(std::min<int64_t>(tiles, sm_count()));
+    auto kern = gemm_tcgen05_kernel<BN, SPLIT>;
+    BT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(GM_THREADS);
-    cfg.dynamicSmemBytes = gm_smem_bytes<BN>();
+    cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
-    cudaLaunchAttribute attrs[1];
+    cudaLaunchAttribute attrs[2];
     attrs[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attrs[0].val.programmaticStreamSerializationAllowed = 1;
+    attrs[1].id = cudaLaunchAttributeClusterDimension;
+    attrs[1].val.clusterDim.x = static_cast<unsigned>(split);
+    attrs[1].val.clusterDim.y = 1;
+    attrs[1].val.clusterDim.z = 1;
     cfg.attrs = attrs;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = SPLIT ? 2 : 1;
     BT_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, map, map_w, p));
     return BT_OK;
+}
+
+static int gemm_split_max_clusters(int split) {
+    static int cache[9] = {0};
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
+    if (split < 2 || split > 8) return 0;
+    if (cache[split] == 0) {
+        auto kern = gemm_tcgen05_kernel<256, true>;
+        const size_t smem = GM_SMEM_LIMIT - 1024;
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) return 0;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(static_cast<unsigned>(split) * 64);
+        cfg.blockDim = dim3(GM_THREADS);
+        cfg.dynamicSmemBytes = smem;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = static_cast<unsigned>(split);
+        attr.val.clusterDim.y = 1;
+        attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) { cudaGetLastError(); return 0; }
+        cache[split] = n > 0 ? n : -1;
+    }
+    return cache[split] > 0 ? cache[split] : 0;
 }
 
 static int launch_gemm_pair(EncodeTiledFn encode, const CUtensorMap& map, const GemmParams& p, cudaStream_t st);   // gemm_tcgen05_2cta.cuh
@@ -545,10 +672,16 @@ extern "C" int bt_gemm_tiled_i8(const int8_t* Xq, const float* sx, const int32_t
         set_error("bt_gemm_tiled_i8: cuTensorMapEncodeTiled is not available from the driver");
         return BT_ERR_CUDA;
     }
+    // CTA pairs (cta_group::2, 256 x 256 tiles) once there are enough 256-row tiles to fill the GPU
+    const int sms = sm_count();
+    bool pair = M > GM_BM && ceil_div<int64_t>(M, 256) * ceil_div<int64_t>(N, 256) >= (sms / 2) * 55 / 100;
+    if (const char* e = std::getenv("BITTORCH_B200_GEMM_PAIR")) pair = std::atoi(e) != 0;      // testing / tuning override
+    // rows of the activation tile that are copied: all 128, or M rounded up to the 8-row swizzle atom when M is small
+    const int a_rows = (pair || M > GM_BM - 8) ? GM_BM : static_cast<int>(ceil_div<int64_t>(M, 8) * 8);
     CUtensorMap map;
     const cuuint64_t gdim[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(M)};
     const cuuint64_t gstride[1] = {static_cast<cuuint64_t>(K)};
-    const cuuint32_t box[2] = {GM_BK, GM_BM};
+    const cuuint32_t box[2] = {GM_BK, static_cast<cuuint32_t>(a_rows)};
     const cuuint32_t estride[2] = {1, 1};
     CUresult cr = encode(&map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t*>(Xq), gdim, gstride, box, estride,
                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
@@ -564,10 +697,11 @@ extern "C" int bt_gemm_tiled_i8(const int8_t* Xq, const float* sx, const int32_t
     p.KT = static_cast<int>(ceil_div<int64_t>(K, TILE_K));
     p.NB = static_cast<int>(ceil_div<int64_t>(N, TILE_N));
     p.y_dtype = y_dtype;
+    p.a_rows = a_rows;
+    p.nl_log2 = 0;
 
     // the widest output tile that still gives every SM a tile; narrow tiles for small problems
     const int64_t m_tiles = ceil_div<int64_t>(M, GM_BM);
-    const int sms = sm_count();
     int bn = 64;
     if (m_tiles * ceil_div<int64_t>(N, 256) >= sms) bn = 256;
     else if (m_tiles * ceil_div<int64_t>(N, 128) >= sms) bn = 128;
@@ -576,11 +710,20 @@ extern "C" int bt_gemm_tiled_i8(const int8_t* Xq, const float* sx, const int32_t
         if (v == 64 || v == 128 || v == 256) bn = v;
     }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    // CTA pairs (cta_group::2, 256 x 256 tiles) once there are enough 256-row tiles to fill the GPU
-    bool pair = M > GM_BM && ceil_div<int64_t>(M, 256) * ceil_div<int64_t>(N, 256) >= (sms / 2) * 7 / 10;
-    if (const char* e = std::getenv("BITTORCH_B200_GEMM_PAIR")) pair = std::atoi(e) != 0;      // testing / tuning override
     if (pair) return launch_gemm_pair(encode, map, p, st);
-    if (bn == 256) return launch_gemm<256>(encode, map, p, st);
-    if (bn == 128) return launch_gemm<128>(encode, map, p, st);
-    return launch_gemm<64>(encode, map, p, st);
+    // a narrow batch: full-width tiles, K split over a cluster so that the tiles still cover the SMs
+    if (M <= 32) {
+        const int64_t tiles = ceil_div<int64_t>(N, 256);
+        const int k_blocks = static_cast<int>(ceil_div<int64_t>(K, GM_BK));
+        int split = 8;      // the widest split whose clusters are all resident at once
+        while (split > 1 && (tiles > gemm_split_max_clusters(split) || split > k_blocks)) split >>= 1;
+        if (const char* e = std::getenv("BITTORCH_B200_GEMM_SPLIT")) {   // testing / tuning override: 1 disables
+            const int v = std::atoi(e);
+            if ((v == 1 || v == 2 || v == 4 || v == 8) && v <= std::max(1, k_blocks)) split = v;
+        }
+        if (split > 1) return launch_gemm<256, true>(encode, map, p, st, split);
+    }
+    if (bn == 256) return launch_gemm<256, false>(encode, map, p, st);
+    if (bn == 128) return launch_gemm<128, false>(encode, map, p, st);
+    return launch_gemm<64, false>(encode, map, p, st);
 }

@@ -3,10 +3,9 @@
 // Two CTAs of a (2,1,1) cluster share one 256 x 256 output tile.  Each CTA loads its own
 // 128 activation rows (TMA, 128-byte swizzle), unpacks its own HALF of the weight tile
 // (128 columns) into shared memory, and owns the 128 x 256 slice of the accumulator that
-// lives in its tensor memory; one thread of the even ("leader") CTA issues the MMAs for
-// the pair.  Compared with the one-CTA kernel, every CTA stores half as many unpacked weight
-// bytes and the tensor core reads half as many B bytes per CTA, which brings the
-// shared-memory traffic per K block from 112 KB to 72 KB (the MMA time covers 64 KB).
+// lives in its tensor memory; one elected lane of the even ("leader") CTA issues the MMAs for
+// the pair.  Compared with the one-CTA kernel, every CTA unpacks and stores half as many weight
+// bytes per MMA, and the pair fetches every activation tile once for 256 columns.
 //
 // Synchronisation (all mbarriers; waits are bounded):
 //   full_a[NL]    leader only   <- TMA bytes of BOTH CTAs' activation tiles
@@ -42,14 +41,6 @@ __device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* m
         ::"r"(smem_u32(dst)), "l"(map), "r"(leader_bar), "r"(x), "r"(y)
         : "memory");
 }
-__device__ __forceinline__ void umma_i8_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
 // Arrives on the barrier at this offset in BOTH CTAs once every MMA issued so far has completed.
 __device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
@@ -60,11 +51,6 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
 // async proxy (after fence.proxy.async) or through tensor memory (after tcgen05.fence), not by generic loads.
 __device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
     asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-__device__ __forceinline__ uint32_t map_to_rank(const void* local_smem_ptr, uint32_t cta_rank) {
-    uint32_t remote;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(local_smem_ptr)), "r"(cta_rank));
-    return remote;
 }
 
 __global__ void __launch_bounds__(GM_THREADS, 1)
@@ -86,10 +72,6 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
     uint32_t* s_tmem = reinterpret_cast<uint32_t*>(tmem_empty + 2);
     __shared__ int s_abort_storage;
     volatile int* s_abort = &s_abort_storage;
-#ifdef BT_TRACE
-    __shared__ long long s_issue_time[G2_NL];
-    volatile long long* issue_time = s_issue_time;
-#endif
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();             // 0 = leader, 1 = peer
@@ -129,56 +111,26 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
     const uint32_t tmem_base = *s_tmem;
     pdl_launch_dependents();
     pdl_wait();
-#ifdef BT_TRACE
-    const int knob = g_knob;
-#endif
 
     if (warp == 0) {
         // ================= producer (both CTAs) =================
         if (lane == 0) {
             RingPos ld;
-#ifdef BT_TRACE
-            long long t_w = 0, n_w = 0;
-#endif
             for (int tile = pair; tile < total_tiles && !*s_abort; tile += n_pairs) {
                 const int mt = tile % m_tiles, nt = tile / m_tiles;
                 const int nb0 = nt * (G2_BN / TILE_N) + static_cast<int>(rank) * G2_P_TILES;
                 bool ok = true;
                 for (int kb = 0; kb < k_blocks; ++kb) {
-#ifdef BT_TRACE
-                    const long long p0 = clock64();
-#endif
                     if (!wait_or_abort(&empty_load[ld.s], ld.phase ^ 1, s_abort)) { ok = false; break; }
-#ifdef BT_TRACE
-                    t_w += clock64() - p0; n_w += 1;
-                    issue_time[ld.s] = clock64();
-#endif
-#ifdef BT_TRACE
-                    if ((knob & 2) && n_w > NL) {
-                        if (leader) mbar_arrive(&full_a[ld.s]);
-                    } else
-#endif
-                    {
                     if (leader) mbar_expect_tx(&full_a[ld.s], 2 * GM_A_BYTES);
                     tma_load_2d_pair(s_a + ld.s * GM_A_BYTES, &map_x, kb * GM_BK, mt * 256 + static_cast<int>(rank) * GM_BM,
                                      smem_u32(&full_a[ld.s]) & G2_PEER_BIT_MASK);
-                    }
-#ifdef BT_TRACE
-                    if ((knob & 8) && n_w > NL) {
-                        mbar_arrive(&full_p[ld.s]);
-                    } else
-#endif
-                    {
                     mbar_expect_tx(&full_p[ld.s], G2_P_BYTES);      // column blocks past the end arrive as zeros
                     tma_load_2d(s_p + ld.s * G2_P_BYTES, &map_w, kb * (TILE_BYTES / 4), nb0, &full_p[ld.s]);
-                    }
                     ld.advance(NL);
                 }
                 if (!ok) break;
             }
-#ifdef BT_TRACE
-            if (blockIdx.x == 0) { g_trace[109] += t_w; g_trace[110] += n_w; }
-#endif
         }
     } else if (warp == 1) {
         // ================= MMA issuer (leader CTA only) =================
@@ -189,10 +141,6 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
             const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem_base, 0);   // the same value, provably warp-uniform
             uint32_t cnt = 0, tcount = 0;      // K blocks / tiles issued so far
             bool ready = false;
-#ifdef BT_TRACE
-            long long n_block = 0;
-            const long long t_start = clock64();
-#endif
             for (int tile = pair; tile < total_tiles; tile += n_pairs, ++tcount) {
                 if (__any_sync(0xffffffffu, *s_abort != 0)) break;
                 const uint32_t a = tcount & 1;
@@ -202,9 +150,6 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
                 bool ok = true;
                 for (int kb = 0; kb < k_blocks; ++kb) {
                     const uint32_t sl = cnt & (NL - 1), sb = cnt & (NB - 1), nx = cnt + 1, nsl = nx & (NL - 1), nsb = nx & (NB - 1);
-#ifdef BT_TRACE
-                    n_block += ready ? 0 : 1;
-#endif
                     if (!ready && (!wait_or_abort_warp(&full_a[sl], (cnt / NL) & 1, s_abort) || !wait_or_abort_warp(&full_b[sb], (cnt / NB) & 1, s_abort))) { ok = false; break; }
                     tc_fence_after();
                     uint32_t polled = 0;
@@ -219,9 +164,6 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
                 if (elect_one_lane()) umma_commit_pair(&tmem_full[a]);
                 __syncwarp();
             }
-#ifdef BT_TRACE
-            if (blockIdx.x == 0 && lane == 0) { g_trace[102] += cnt; g_trace[104] += tcount; g_trace[111] += n_block; g_trace[112] += clock64() - t_start; }
-#endif
         }
     } else if (warp < 2 + GM_EPI_WARPS) {
         // ================= epilogue (both CTAs, own 128 rows) =================
@@ -239,9 +181,6 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
 #pragma unroll 1
             for (int c0 = 0; c0 < G2_BN; c0 += 32) {
                 int v[32];
-#ifdef BT_TRACE
-                if (!(knob & 32))
-#endif
                 {
                 tmem_ld_32x32b_x32(taddr + c0, v);
                 tmem_ld_wait();
@@ -249,12 +188,9 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
                 if (c0 + 32 == G2_BN) {
                     tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive_remote(map_to_rank(&tmem_empty[a], 0));
+                    if (lane == 0) mbar_arrive_remote(map_to_cta(&tmem_empty[a], 0));
                 }
                 const int n0 = nt * G2_BN + c0;
-#ifdef BT_TRACE
-                if (knob & 4) continue;
-#endif
                 if (m < p.M && n0 < p.N) {
 #pragma unroll
                     for (int c = 0; c < 32; ++c) v[c] -= xs;
@@ -283,28 +219,12 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
         ld.advance_by(NL, grp);
         bb.advance_by(NB, grp);
         uint32_t kcount = grp, kseen = 0;
-#ifdef BT_TRACE
-        long long t_p = 0, t_eb = 0, t_u = 0, n_u = 0, t_f = 0, t_ar = 0, t_lat_p = 0, n_lat_p = 0;
-#endif
         for (int tile = pair; tile < total_tiles && !*s_abort; tile += n_pairs, kseen += k_blocks) {
             bool ok = true;
             for (; kcount < kseen + k_blocks; kcount += GM_UNPACK_GROUPS) {
-#ifdef BT_TRACE
-                const long long u0 = clock64();
-                if (!wait_or_abort(&full_p[ld.s], ld.phase, s_abort)) { ok = false; break; }
-                const long long u1 = clock64();
-                if (!wait_or_abort(&empty_b[bb.s], bb.phase ^ 1, s_abort)) { ok = false; break; }
-                const long long u2 = clock64();
-                t_p += u1 - u0; t_eb += u2 - u1; n_u += 1;
-                if (u1 - u0 > 60) { t_lat_p += u1 - issue_time[ld.s]; n_lat_p += 1; }
-#else
                 if (!wait_or_abort(&full_p[ld.s], ld.phase, s_abort) || !wait_or_abort(&empty_b[bb.s], bb.phase ^ 1, s_abort)) { ok = false; break; }
-#endif
                 const uint8_t* pk = s_p + ld.s * G2_P_BYTES;
                 uint8_t* bt = s_b + bb.s * G2_B_BYTES;
-#ifdef BT_TRACE
-                if (!(knob & 1))
-#endif
 #pragma unroll
                 for (int tix = gwarp; tix < G2_P_TILES; tix += GM_GROUP_WARPS) {
                     const uint4 wv = *reinterpret_cast<const uint4*>(pk + tix * TILE_BYTES + lane * 16);
@@ -324,27 +244,14 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
                         }
                     }
                 }
-#ifdef BT_TRACE
-                const long long u3 = clock64();
-#endif
                 fence_proxy_async_smem();
-#ifdef BT_TRACE
-                const long long u4 = clock64();
-#endif
                 __syncwarp();
-                if (lane == 0) mbar_arrive_remote(map_to_rank(&full_b[bb.s], 0));
-#ifdef BT_TRACE
-                const long long u5 = clock64();
-                t_u += u3 - u2; t_f += u4 - u3; t_ar += u5 - u4;
-#endif
+                if (lane == 0) mbar_arrive_remote(map_to_cta(&full_b[bb.s], 0));
                 ld.advance_by(NL, GM_UNPACK_GROUPS);
                 bb.advance_by(NB, GM_UNPACK_GROUPS);
             }
             if (!ok) break;
         }
-#ifdef BT_TRACE
-        if (blockIdx.x == 0 && utid == 0) { g_trace[105] += t_p; g_trace[106] += t_eb; g_trace[107] += n_u; g_trace[108] += t_u; g_trace[113] += t_f; g_trace[114] += t_ar; g_trace[117] += t_lat_p; g_trace[118] += n_lat_p; }
-#endif
     }
 
     tc_fence_before();

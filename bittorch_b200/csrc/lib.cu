@@ -76,11 +76,6 @@ extern "C" int bt_trace_read(unsigned long long* out64) {
     BT_CUDA_OK(cudaMemcpyFromSymbol(out64, g_trace, sizeof(unsigned long long) * 128));
     return BT_OK;
 }
-extern "C" int bt_trace_set_knob(int v) {
-    using namespace bt;
-    BT_CUDA_OK(cudaMemcpyToSymbol(g_knob, &v, sizeof(int)));
-    return BT_OK;
-}
 extern "C" int bt_trace_read_cta(unsigned long long* out64, unsigned int* sm) {
     using namespace bt;
     BT_CUDA_OK(cudaDeviceSynchronize());

@@ -138,6 +138,20 @@ def test_gemm_cta_pair_kernel_bit_exact(oracle, m, k, n, monkeypatch):
     assert np.array_equal(y.numpy().view(np.uint32), y_ref.view(np.uint32))
 
 
+@pytest.mark.parametrize("split", ["1", "2", "4", "8"])
+@pytest.mark.parametrize("m,k,n", [(1, 4096, 4096), (16, 4096, 11008), (32, 2560, 6912), (5, 1024, 300), (17, 128, 256),
+                                   (9, 48, 70), (20, 8192, 512), (3, 16, 5), (32, 1040, 513)])
+def test_gemm_narrow_batch_every_k_split_gives_the_same_bits(oracle, m, k, n, split, monkeypatch):
+    """Up to 32 rows: full-width tiles with K split over a thread-block cluster, partial accumulators
+    exchanged through distributed shared memory.  Every cluster size gives the oracle's bits."""
+    monkeypatch.setenv("BITTORCH_B200_GEMM_SPLIT", split)
+    prob = _problem(m, k, n, seed=int(split) + m + n)
+    acc_ref, y_ref = _reference(oracle, *prob)
+    y, acc = _run("gemm_tiled_i8", *prob, torch.float32)
+    assert np.array_equal(acc.numpy(), acc_ref)
+    assert np.array_equal(y.numpy().view(np.uint32), y_ref.view(np.uint32))
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_gemm_half_outputs(oracle, dtype):
     prob = _problem(200, 384, 328, seed=5)
