@@ -11,8 +11,10 @@ GEMV; the next layer's input is the first K columns of this layer's output.  The
 CUDA graph whose kernels are chained with programmatic dependent launch.
 
 Metric: achieved HBM GB/s on algorithmic bytes (ceil(K/4)*N + 4N + 2MK + 2MN per layer).
-With --gpus N > 1 the same stack is column-sharded over N ranks and every layer ends in
-an NCCL all-gather of the outputs (strong scaling: total work fixed).
+With --gpus N > 1 every GPU runs its own replica of the stack (weak scaling, no collective: a layer of this
+shape is shorter than any gather).  Column-parallel sharding is timed in the same run on a 70B-shaped layer
+("sharded" in the JSON line): the chain on one GPU against the chain column-sharded over the ranks with an
+NCCL all-gather per layer.
 
 The one JSON line also carries: `roofline` of the dominant kernel (GEMV-only launches),
 `e2e` (host buffers through the public module API), `cpu_baseline` (eager restatement of
@@ -171,6 +173,37 @@ def make_decode_step(stack: LayerStack, m: int, x0: torch.Tensor, group=None):
         return y_loc[-1] if world == 1 else y_all[-1]
 
     return step
+
+
+def run_sharded_section(dev, rank: int, world: int, group, steps: int, warmup: int):
+    """Column-parallel sharding on a layer whose weight stream is long: the 70B-shaped gate/up layer
+    (K=8192 -> N=28672) at M=1, a chain of 8 layers.  Times, in the same run, the chain on one GPU and the chain
+    column-sharded over the ranks with an NCCL all-gather per layer.  Returns (dict for the JSON line, graphs to
+    reset before leaving)."""
+    import torch.distributed as dist
+
+    k5, n5, l5, m = 8192, 28672, 8, 1
+    x0 = torch.randn(m, k5, generator=torch.Generator().manual_seed(5)).to(torch.bfloat16).to(dev)
+
+    def timed(step_fn):
+        graph, y = capture(step_fn)
+        ms = time_replays(graph, steps, warmup, dist.barrier)
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return graph, y, float(t.item()) / steps * 1e3 / l5          # us per layer, slowest rank
+
+    full = LayerStack(l5, k5, n5, dev, 0, 1, seed=7)
+    g_full, _, us_single = timed(make_decode_step(full, m, x0, None))
+    g_full.reset()
+    del full
+    shard = LayerStack(l5, k5, n5, dev, rank, world, seed=7)
+    g_nccl, _, us_nccl = timed(make_decode_step(shard, m, x0, group))
+    layer_bytes = algorithmic_bytes(m, k5, n5)
+    out = {"workload": f"70B-shaped decode chain: M=1 bf16, {l5} layers of K={k5}->N={n5}, columns sharded over {world} GPUs",
+           "us_per_layer_single_gpu": us_single, "us_per_layer_sharded_nccl_all_gather": us_nccl,
+           "gbs_single_gpu": layer_bytes / us_single / 1e3, "gbs_sharded_nccl_all_gather": layer_bytes / us_nccl / 1e3,
+           "speedup_sharded_vs_single_gpu": us_single / us_nccl}
+    return out, [g_nccl]
 
 
 def capture(step_fn, warm: int = 3):
@@ -492,9 +525,12 @@ def main() -> None:
         group = dist.group.WORLD
     peaks = load_peaks()
 
-    stack = LayerStack(LAYERS, K_IN, N_OUT, dev, rank, world, seed=0)
+    # At N > 1 every GPU runs its own replica of the stack (independent decode streams, no collective): for this
+    # shape a layer is shorter than any gather.  Column-parallel sharding is measured under "sharded" below, on a
+    # layer that is long enough for it.
+    stack = LayerStack(LAYERS, K_IN, N_OUT, dev, 0, 1, seed=0)
     x0 = torch.randn(M_TOK, K_IN, generator=torch.Generator().manual_seed(1)).to(torch.bfloat16).to(dev)
-    step = make_decode_step(stack, M_TOK, x0, group)
+    step = make_decode_step(stack, M_TOK, x0, None)
     graph, _ = capture(step)
 
     def barrier():
@@ -508,7 +544,7 @@ def main() -> None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = float(t.item())
     ms_per_step = ms / args.steps
-    bytes_per_step = LAYERS * algorithmic_bytes(M_TOK, K_IN, N_OUT)       # whole job, all ranks together
+    bytes_per_step = LAYERS * algorithmic_bytes(M_TOK, K_IN, N_OUT) * world     # whole job: one stack per GPU
     value = bytes_per_step / (ms_per_step * 1e-3) / 1e9
     launches_per_step = LAYERS            # one fused quantize+GEMV kernel per layer
 
@@ -533,8 +569,7 @@ def main() -> None:
     if world > 1:
         dist.all_reduce(te, op=dist.ReduceOp.MAX)
     e_ms_step = float(te.item()) / args.steps
-    # at N > 1 the e2e leg runs each rank's shard chain without the gather: local bytes x ranks
-    e2e_bytes = LAYERS * algorithmic_bytes(M_TOK, K_IN, stack.n_local) * world
+    e2e_bytes = LAYERS * algorithmic_bytes(M_TOK, K_IN, N_OUT) * world
     e2e = {"value": e2e_bytes / (e_ms_step * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e_ms_step,
            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
 
@@ -542,15 +577,20 @@ def main() -> None:
     line = {
         "metric": "packed_ternary_gemv_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+        "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
         "config": {"workload": WORKLOAD, "M": M_TOK, "K": K_IN, "N": N_OUT, "layers": LAYERS,
                    "l2": "weights rotate over 32 layers (344 MiB), larger than the 126 MB L2",
-                   "parallelism": "single GPU" if world == 1 else f"column-parallel x{world} + NCCL all-gather per layer",
+                   "parallelism": "single GPU" if world == 1 else
+                   f"{world} replicas of the stack, one per GPU, no collective (column-parallel sharding: see 'sharded')",
                    "launch": "CUDA graph replay, kernels chained by programmatic dependent launch"},
         "frac_of_measured_hbm": value / (peaks["hbm_gbs"] * world),
-        "roofline": roofline, "e2e": e2e, "gpu_launches": launches_per_step * args.steps,
+        "roofline": roofline, "e2e": e2e, "gpu_launches": launches_per_step * args.steps * world,
         "clocks": clk.result, "device_status": status,
     }
+    keep = None
+    if world > 1:
+        line["sharded"], keep = run_sharded_section(dev, rank, world, group, max(20, args.steps // 4), args.warmup)
+        line["device_status"] = _C.device_status(dev)
 
     if rank == 0 and world == 1 and not args.no_sweep:
         sec, reps, threads = cpu_reference_layer_seconds()
@@ -575,6 +615,8 @@ def main() -> None:
         torch.cuda.synchronize()
         dist.barrier()
         graph.reset()
+        for g in keep or []:
+            g.reset()
         sys.stdout.flush()
         sys.stderr.flush()
         os._exit(0)

@@ -73,6 +73,28 @@ def test_against_oracle_large(oracle, n, k, seed):
     assert np.array_equal(out["packed_T"].numpy(), oracle.pack_transposed(codes_ref))
 
 
+@pytest.mark.parametrize("dtype_code", [0, 1, 2])
+def test_special_rows_in_every_dtype(oracle, dtype_code):
+    """NaN and Inf rows, a row of zeros and a partial last group of rows, in fp32 / fp16 / bf16 masters
+    (the arithmetic runs in the storage type), against the oracle."""
+    from bittorch_b200 import _C
+
+    for (n, k, seed) in [(4096, 4096, 1), (37, 1024, 2), (4, 8192, 3), (1001, 2560, 4), (130, 11008, 5)]:
+        g = torch.Generator().manual_seed(seed)
+        w = torch.randn(n, k, generator=g)
+        w[0, 3] = float("nan")
+        w[1, 5] = float("inf")
+        w[2, :] = 0.0
+        w = w.to(DT[dtype_code])
+        codes_ref, scale_ref = oracle.ternarize(w.float().numpy(), 0.05, dtype=dtype_code)
+        out = _C.quantize_pack(w.cuda(), 0.05, want_packed=True, want_codes=True, want_tern=True)
+        torch.cuda.synchronize()
+        assert _C.device_status() == 0
+        assert np.array_equal(out["codes"].cpu().numpy(), codes_ref)
+        assert _bits_equal(out["scale"].cpu().numpy(), scale_ref)
+        assert np.array_equal(out["packed_T"].cpu().numpy(), oracle.pack_transposed(codes_ref))
+
+
 def test_strided_rows_and_optional_outputs():
     from bittorch_b200 import _C
 
