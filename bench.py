@@ -432,7 +432,7 @@ def run_sweep(peaks, dev):
         for m in (1, 4, 16, 256, 2048):
             ms = time_kernel_only(stack, m, reps=10 if m <= 16 else 3)
             row = {"K": k, "N": n, "M": m, "us": ms * 1e3}
-            if m <= 16:     # decode sizes are judged on bytes streamed
+            if m <= 16:     # decode sizes are measured in bytes streamed
                 gbs = algorithmic_bytes(m, k, n) / (ms * 1e-3) / 1e9
                 row.update({"kernel": "gemv_tiled" if m <= 4 else "gemm_tcgen05", "gbs": gbs,
                             "frac_hbm_measured": gbs / peaks["hbm_gbs"], "frac_hbm_nominal_8tbs": gbs / 8000.0})

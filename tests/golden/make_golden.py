@@ -2,7 +2,7 @@
 
 Run where the reference checkout is mounted (it is imported, never copied):
 
-    PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py [/path/to/reference]
+    PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py /path/to/reference
 
 Everything is computed on CPU with the reference's own public functions
 (``bittorch.quant.ternary_quantize``, ``pack_ternary[_transposed]``,
@@ -21,7 +21,9 @@ import numpy as np
 import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("BITTORCH_REFERENCE", "")
+if not REF:
+    raise SystemExit("usage: make_golden.py <path to a checkout of the reference> (or set BITTORCH_REFERENCE)")
 sys.path.insert(0, REF)
 warnings.filterwarnings("ignore")
 
