@@ -1,0 +1,208 @@
+"""LLaMA-style ternary decoder: the caller of the ternary linear layers in a language model.
+
+The reference's Python package stops at the layer; its only transformer is the browser runtime
+(js/src/models/TernaryTransformer.ts).  This module restates that model's structure on top of the
+layers of this package so that the kernels can be driven the way a model drives them (prefill over a
+prompt, then one token at a time against a key/value cache):
+
+* pre-norm blocks: ``x += attn(rmsnorm(x)); x += swiglu(rmsnorm(x))`` (TernaryTransformer.ts:366-464);
+* RMSNorm with eps 1e-5 inside the square root (js/src/core/RMSNorm.ts:10-38);
+* rotary embedding, theta 1e4, pairing element i with i + head_dim/2 (js/src/core/RoPE.ts:10-92),
+  applied to the queries and to the keys as they enter the cache;
+* grouped-query attention with one fused key/value projection whose output is ``[K | V]``
+  (TernaryTransformer.ts:553-600);
+* SwiGLU: ``w_down(silu(w_gate(x)) * w_up(x))`` (:520-550);
+* every projection a bias-free ternary linear; embedding ``tok``, final ``norm`` and ``head`` in floating point;
+* parameter names of the runtime's checkpoint (:141-188): ``tok.weight``, ``blocks.{i}.norm1.weight``,
+  ``blocks.{i}.attn.{q_proj,kv_proj,proj}``, ``blocks.{i}.norm2.weight``, ``blocks.{i}.mlp.{w_gate,w_up,w_down}``,
+  ``norm.weight``, ``head.weight``; after ``to_inference()`` the ternary layers hold ``weight_packed`` / ``scale``.
+
+The layers are built as ``TernaryLinear`` (trainable masters; ``backend="python"`` runs anywhere);
+``to_inference()`` swaps them for packed ``TernaryLinearInference`` layers on a CUDA device.
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import List, Optional, Tuple
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+from torch import Tensor
+
+from ..nn import TernaryLinear
+
+NORM_EPS = 1e-5
+ROPE_THETA = 10000.0
+
+
+@dataclass
+class DecoderConfig:
+    vocab_size: int
+    dim: int
+    n_layers: int
+    n_heads: int
+    ffn_dim: int
+    max_seq_len: int
+    n_kv_heads: Optional[int] = None          # defaults to n_heads (TernaryTransformer.ts:116)
+    threshold_factor: float = 0.05
+    backend: str = "auto"
+
+    def __post_init__(self) -> None:
+        if self.n_kv_heads is None:
+            self.n_kv_heads = self.n_heads
+        if self.dim % self.n_heads or self.n_heads % self.n_kv_heads or (self.dim // self.n_heads) % 2:
+            raise ValueError("dim must divide into an even head size and n_heads into n_kv_heads groups")
+
+    @property
+    def head_dim(self) -> int:
+        return self.dim // self.n_heads
+
+
+class RMSNorm(nn.Module):
+    """``x / sqrt(mean(x^2) + eps) * weight`` (js/src/core/RMSNorm.ts:10-38)."""
+
+    def __init__(self, dim: int) -> None:
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(dim))
+
+    def forward(self, x: Tensor) -> Tensor:
+        xf = x.float()
+        rms = torch.sqrt(xf.pow(2).mean(dim=-1, keepdim=True) + NORM_EPS)
+        return ((xf / rms) * self.weight.float()).to(x.dtype)
+
+
+def rope_tables(max_seq_len: int, head_dim: int, device=None) -> Tuple[Tensor, Tensor]:
+    """cos / sin of ``pos * theta^(-2i/head_dim)``, shape [max_seq_len, head_dim/2] (js/src/core/RoPE.ts:25-49)."""
+    half = head_dim // 2
+    freq = 1.0 / torch.pow(torch.tensor(ROPE_THETA, dtype=torch.float64), torch.arange(half, dtype=torch.float64) * 2 / head_dim)
+    angle = torch.arange(max_seq_len, dtype=torch.float64)[:, None] * freq[None, :]
+    return angle.cos().float().to(device), angle.sin().float().to(device)
+
+
+def apply_rope(x: Tensor, cos: Tensor, sin: Tensor, pos0: int) -> Tensor:
+    """x: [B, H, T, head_dim]; rotates (x[i], x[i + half]) by the angle of position pos0 + t (RoPE.ts:65-92)."""
+    t = x.shape[2]
+    half = x.shape[3] // 2
+    c = cos[pos0:pos0 + t][None, None].to(x.dtype)
+    s = sin[pos0:pos0 + t][None, None].to(x.dtype)
+    x0, x1 = x[..., :half], x[..., half:]
+    return torch.cat([x0 * c - x1 * s, x0 * s + x1 * c], dim=-1)
+
+
+class Attention(nn.Module):
+    def __init__(self, cfg: DecoderConfig) -> None:
+        super().__init__()
+        self.cfg = cfg
+        kv_dim = cfg.n_kv_heads * cfg.head_dim
+        mk = lambda i, o: TernaryLinear(i, o, bias=False, threshold_factor=cfg.threshold_factor, backend=cfg.backend)
+        self.q_proj = mk(cfg.dim, cfg.dim)
+        self.kv_proj = mk(cfg.dim, 2 * kv_dim)           # output [K | V], heads contiguous inside each half
+        self.proj = mk(cfg.dim, cfg.dim)
+
+    def forward(self, x: Tensor, cache: Tuple[Tensor, Tensor], pos0: int, cos: Tensor, sin: Tensor) -> Tensor:
+        cfg = self.cfg
+        b, t, _ = x.shape
+        hd, nh, nkv = cfg.head_dim, cfg.n_heads, cfg.n_kv_heads
+        q = self.q_proj(x).view(b, t, nh, hd).transpose(1, 2)                    # [B, H, T, hd]
+        kv = self.kv_proj(x).view(b, t, 2, nkv, hd)
+        k = kv[:, :, 0].transpose(1, 2)                                          # [B, Hkv, T, hd]
+        v = kv[:, :, 1].transpose(1, 2)
+        q = apply_rope(q, cos, sin, pos0)
+        k_cache, v_cache = cache                                                 # [B, Hkv, max_seq_len, hd]
+        k_cache[:, :, pos0:pos0 + t] = apply_rope(k, cos, sin, pos0).to(k_cache.dtype)   # keys are stored rotated
+        v_cache[:, :, pos0:pos0 + t] = v.to(v_cache.dtype)
+        keys = k_cache[:, :, :pos0 + t].to(q.dtype)
+        vals = v_cache[:, :, :pos0 + t].to(q.dtype)
+        if nkv != nh:
+            keys = keys.repeat_interleave(nh // nkv, dim=1)                      # query head h reads kv head h // group
+            vals = vals.repeat_interleave(nh // nkv, dim=1)
+        # query at position pos0 + i sees keys 0 .. pos0 + i
+        mask = torch.ones(t, pos0 + t, dtype=torch.bool, device=x.device).tril(diagonal=pos0)
+        out = F.scaled_dot_product_attention(q, keys, vals, attn_mask=mask, scale=1.0 / math.sqrt(hd))
+        return self.proj(out.transpose(1, 2).reshape(b, t, cfg.dim))
+
+
+class SwiGLU(nn.Module):
+    def __init__(self, cfg: DecoderConfig) -> None:
+        super().__init__()
+        mk = lambda i, o: TernaryLinear(i, o, bias=False, threshold_factor=cfg.threshold_factor, backend=cfg.backend)
+        self.w_gate = mk(cfg.dim, cfg.ffn_dim)
+        self.w_up = mk(cfg.dim, cfg.ffn_dim)
+        self.w_down = mk(cfg.ffn_dim, cfg.dim)
+
+    def forward(self, x: Tensor) -> Tensor:
+        return self.w_down(F.silu(self.w_gate(x)) * self.w_up(x))
+
+
+class Block(nn.Module):
+    def __init__(self, cfg: DecoderConfig) -> None:
+        super().__init__()
+        self.norm1 = RMSNorm(cfg.dim)
+        self.attn = Attention(cfg)
+        self.norm2 = RMSNorm(cfg.dim)
+        self.mlp = SwiGLU(cfg)
+
+    def forward(self, x: Tensor, cache, pos0: int, cos: Tensor, sin: Tensor) -> Tensor:
+        x = x + self.attn(self.norm1(x), cache, pos0, cos, sin)
+        return x + self.mlp(self.norm2(x))
+
+
+class TernaryDecoder(nn.Module):
+    """Token ids -> logits, with a key/value cache for one-token-at-a-time decoding."""
+
+    def __init__(self, cfg: DecoderConfig) -> None:
+        super().__init__()
+        self.cfg = cfg
+        self.tok = nn.Embedding(cfg.vocab_size, cfg.dim)
+        self.blocks = nn.ModuleList(Block(cfg) for _ in range(cfg.n_layers))
+        self.norm = RMSNorm(cfg.dim)
+        self.head = nn.Linear(cfg.dim, cfg.vocab_size, bias=False)
+        cos, sin = rope_tables(cfg.max_seq_len, cfg.head_dim)
+        self.register_buffer("rope_cos", cos, persistent=False)
+        self.register_buffer("rope_sin", sin, persistent=False)
+
+    def new_cache(self, batch: int, dtype: Optional[torch.dtype] = None) -> List[Tuple[Tensor, Tensor]]:
+        cfg = self.cfg
+        dev = self.tok.weight.device
+        dtype = dtype or self.tok.weight.dtype
+        shape = (batch, cfg.n_kv_heads, cfg.max_seq_len, cfg.head_dim)
+        return [(torch.zeros(shape, dtype=dtype, device=dev), torch.zeros(shape, dtype=dtype, device=dev)) for _ in self.blocks]
+
+    def forward(self, tokens: Tensor, cache: Optional[list] = None, pos0: int = 0) -> Tensor:
+        """tokens: [B, T] ids at positions pos0 .. pos0+T-1 -> logits [B, T, vocab]; ``cache`` (from ``new_cache``)
+        is filled in place; without one the call is a stand-alone pass over the whole sequence."""
+        b, t = tokens.shape
+        if pos0 + t > self.cfg.max_seq_len:
+            raise ValueError(f"positions up to {pos0 + t} exceed max_seq_len={self.cfg.max_seq_len}")
+        if cache is None:
+            if pos0 != 0:
+                raise ValueError("a pass that does not start at position 0 needs the cache of the earlier positions")
+            cache = self.new_cache(b)
+        x = self.tok(tokens)
+        for block, layer_cache in zip(self.blocks, cache):
+            x = block(x, layer_cache, pos0, self.rope_cos, self.rope_sin)
+        return self.head(self.norm(x))
+
+    @torch.no_grad()
+    def generate_greedy(self, prompt: Tensor, new_tokens: int) -> Tensor:
+        """Prefill over ``prompt`` [B, T], then ``new_tokens`` greedy steps against the cache -> [B, T + new_tokens]."""
+        b, t = prompt.shape
+        cache = self.new_cache(b)
+        out = [prompt]
+        nxt = self.forward(prompt, cache, 0)[:, -1].argmax(dim=-1, keepdim=True)
+        for i in range(new_tokens):
+            out.append(nxt)
+            if i + 1 < new_tokens:
+                nxt = self.forward(nxt, cache, t + i)[:, -1].argmax(dim=-1, keepdim=True)
+        return torch.cat(out, dim=1)
+
+    def to_inference(self) -> "TernaryDecoder":
+        """Replaces every ternary projection by its packed inference form (2-bit weights, fused kernels); the
+        model must be on a CUDA device.  ``tok``, the norms and ``head`` stay in floating point."""
+        from .convert import convert_linear_layers
+
+        convert_linear_layers(self, skip_names=["head"], inplace=True)
+        return self
