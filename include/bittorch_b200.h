@@ -169,6 +169,10 @@ int bt_gemv_tiled(const void* X, int x_dtype, int64_t M, int64_t K, int64_t ldx,
  * mma.sync kernel (csrc/kernels/ternary_gemm_tensor_core.cu:349-657).
  * xsum int32 [M]: per-row sums of Xq, as written by bt_act_quant_i8 (required).
  * K must be a multiple of 16 (row pitch of the TMA descriptor over Xq).
+ * Three kernels behind this entry, chosen by shape: CTA pairs (tcgen05.mma.cta_group::2, 256 x 256
+ * tiles) when there are enough such tiles; one CTA per 128 x {256,128,64} tile otherwise; and, up to
+ * 32 rows, full-width tiles with K split over a thread-block cluster whose partial accumulators meet
+ * in distributed shared memory.  None uses global scratch memory; results do not depend on the choice.
  */
 int bt_gemm_tiled_i8(const int8_t* Xq, const float* sx, const int32_t* xsum, int64_t M, int64_t K,
                      const uint8_t* tiled, int64_t N, const float* scale, const float* bias,
