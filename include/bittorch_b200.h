@@ -144,8 +144,8 @@ int bt_gemv_tiled_i8(const int8_t* Xq, const float* sx, int64_t M, int64_t K,
 
 /*
  * Decode-size packed ternary linear straight from floating-point activations: the
- * per-token int8 quantizer of bt_act_quant_i8 runs inside the GEMV kernel (each CTA
- * reduces |x| over its K slice, the thread-block cluster exchanges the partial maxima),
+ * per-token int8 quantizer of bt_act_quant_i8 runs inside the GEMV kernel (every CTA
+ * quantizes the few activation rows itself, into shared memory, while its weights stream in),
  * so a decode layer is ONE dependent kernel launch.  Results are bit-identical to
  * bt_act_quant_i8 followed by bt_gemv_tiled_i8.
  * Replaces the quantize-inside-the-GEMM structure of the reference's integer kernel
