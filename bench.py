@@ -589,8 +589,12 @@ def main() -> None:
     }
     keep = None
     if world > 1:
-        line["sharded"], keep = run_sharded_section(dev, rank, world, group, max(20, args.steps // 4), args.warmup)
-        line["device_status"] = _C.device_status(dev)
+        # a secondary measurement: whatever happens in it, the line above is still printed
+        try:
+            line["sharded"], keep = run_sharded_section(dev, rank, world, group, max(20, args.steps // 4), args.warmup)
+            line["device_status"] = _C.device_status(dev)
+        except Exception as exc:      # noqa: BLE001
+            line["sharded"] = {"error": f"{type(exc).__name__}: {exc}"[:300]}
 
     if rank == 0 and world == 1 and not args.no_sweep:
         sec, reps, threads = cpu_reference_layer_seconds()
@@ -612,11 +616,14 @@ def main() -> None:
         # Tearing the NCCL communicator down while CUDA graphs that captured its collectives are
         # still alive blocks forever, so: drop the graph, synchronise, and leave without the
         # (optional) destroy_process_group.
-        torch.cuda.synchronize()
-        dist.barrier()
-        graph.reset()
-        for g in keep or []:
-            g.reset()
+        try:
+            torch.cuda.synchronize()
+            dist.barrier()
+            graph.reset()
+            for g in keep or []:
+                g.reset()
+        except Exception:             # noqa: BLE001  (leaving anyway)
+            pass
         sys.stdout.flush()
         sys.stderr.flush()
         os._exit(0)

@@ -1,12 +1,13 @@
 // Prefill-size packed ternary linear on int8 activations: tcgen05 (5th-gen tensor core)
 // GEMM with accumulators in tensor memory.
 //
-// Persistent kernel, one CTA per SM, output tile 128 (rows of X) x 256 (output columns),
+// Persistent kernel, one CTA per SM, output tile 128 (rows of X) x BN (output columns, 256 / 128 / 64),
 // K consumed in blocks of 128.  Warp roles:
-//   warp 0       producer: TMA tensor load of the int8 activation tile (128 x 128 B,
-//                128-byte swizzle) and 1-D bulk copies of the 2-bit weight tiles (8 KB)
-//   warp 1       MMA issuer: 4 x tcgen05.mma.kind::i8 (128x256x32) per K block, commits
-//                free the stage / publish the accumulator
+//   warp 0       producer: two TMA tensor loads per K block: the int8 activation tile (up to 128 rows x 128 B,
+//                128-byte swizzle) and the block's 2-bit weight tiles (the tiled buffer seen as [column block][K])
+//   warp 1       MMA issuer: the whole warp runs the loop, one elected lane issues each K block as one
+//                instruction burst (4 x tcgen05.mma.kind::i8 128xBNx32, polls of the next block's barriers,
+//                commits that free the stage / publish the accumulator)
 //   warps 2-5    epilogue: tcgen05.ld of the int32 accumulators, un-scale, dequantise, store
 //   warps 6-13   unpack: 2-bit tiles -> unsigned bytes t+1 in the K-major 128-byte-swizzled B tile
 // Weights enter the MMA as u8 codes t+1 (one shift and one mask per four weights, four
@@ -14,6 +15,9 @@
 // int8 activations, which the activation quantizer provides.
 // Accumulators are double-buffered in the 512 TMEM columns so the epilogue of one tile
 // overlaps the main loop of the next.
+// A second instantiation (SPLIT) serves batches of up to 32 rows: one 128 x 256 tile per thread-block
+// cluster, K split over the cluster's CTAs, partial accumulators exchanged through distributed shared memory.
+// The CTA-pair kernel (cta_group::2) for large batches is in gemm_tcgen05_2cta.cuh.
 // Algorithmic work per call: 2*M*N*K integer ops.
 #pragma once
 
