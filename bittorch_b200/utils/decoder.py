@@ -32,7 +32,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 from torch import Tensor
 
-from ..nn import TernaryLinear
+from ..nn import TernaryLinear, TernaryLinearInference
 
 NORM_EPS = 1e-5
 ROPE_THETA = 10000.0
@@ -92,6 +92,44 @@ def apply_rope(x: Tensor, cos: Tensor, sin: Tensor, pos0: int) -> Tensor:
     return torch.cat([x0 * c - x1 * s, x0 * s + x1 * c], dim=-1)
 
 
+def fuse_inference_columns(layers) -> TernaryLinearInference:
+    """Packed layers that read the same input, as ONE layer with their output columns side by side.  Columns of a
+    packed ternary layer are independent (own bytes, own scale; the activation quantizer depends on the input
+    only), so the fused layer's outputs are the members' outputs concatenated, bit for bit - and a decode step
+    pays one dependent kernel launch instead of one per member."""
+    k = layers[0].in_features
+    if any(l.in_features != k for l in layers):
+        raise ValueError("fused layers must read the same input")
+    wp = torch.cat([l.weight_packed for l in layers], dim=1).contiguous()
+    scale = torch.cat([l.scale for l in layers])
+    bias = None
+    if any(l.bias is not None for l in layers):
+        bias = torch.cat([l.bias if l.bias is not None else torch.zeros_like(l.scale) for l in layers])
+    return TernaryLinearInference(k, sum(l.out_features for l in layers), wp, scale, bias)
+
+
+class _FusedColumns:
+    """Runs packed sibling layers as one (``fuse_inference_columns``), rebuilt when a member's buffers change.
+    Not a submodule: the members keep their names and buffers in the state dict."""
+
+    def __init__(self, *layers) -> None:
+        self.layers = layers
+        self._key = None
+        self._fused: Optional[TernaryLinearInference] = None
+
+    @property
+    def usable(self) -> bool:
+        return all(isinstance(l, TernaryLinearInference) for l in self.layers)
+
+    def __call__(self, x: Tensor):
+        key = tuple((l.weight_packed.data_ptr(), l.weight_packed._version, l.scale.data_ptr(), l.scale._version)
+                    for l in self.layers)
+        if key != self._key:
+            self._fused = fuse_inference_columns(self.layers)
+            self._key = key
+        return torch.split(self._fused(x), [l.out_features for l in self.layers], dim=-1)
+
+
 class Attention(nn.Module):
     def __init__(self, cfg: DecoderConfig) -> None:
         super().__init__()
@@ -101,13 +139,20 @@ class Attention(nn.Module):
         self.q_proj = mk(cfg.dim, cfg.dim)
         self.kv_proj = mk(cfg.dim, 2 * kv_dim)           # output [K | V], heads contiguous inside each half
         self.proj = mk(cfg.dim, cfg.dim)
+        self._fused: Optional[_FusedColumns] = None
 
     def forward(self, x: Tensor, cache: Tuple[Tensor, Tensor], pos0: int, cos: Tensor, sin: Tensor) -> Tensor:
         cfg = self.cfg
         b, t, _ = x.shape
         hd, nh, nkv = cfg.head_dim, cfg.n_heads, cfg.n_kv_heads
-        q = self.q_proj(x).view(b, t, nh, hd).transpose(1, 2)                    # [B, H, T, hd]
-        kv = self.kv_proj(x).view(b, t, 2, nkv, hd)
+        if self._fused is None or self._fused.layers != (self.q_proj, self.kv_proj):
+            self._fused = _FusedColumns(self.q_proj, self.kv_proj)
+        if self._fused.usable:                           # packed layers: one launch for both projections
+            q, kv = self._fused(x)
+        else:
+            q, kv = self.q_proj(x), self.kv_proj(x)
+        q = q.reshape(b, t, nh, hd).transpose(1, 2)                              # [B, H, T, hd]
+        kv = kv.reshape(b, t, 2, nkv, hd)
         k = kv[:, :, 0].transpose(1, 2)                                          # [B, Hkv, T, hd]
         v = kv[:, :, 1].transpose(1, 2)
         q = apply_rope(q, cos, sin, pos0)
@@ -132,9 +177,16 @@ class SwiGLU(nn.Module):
         self.w_gate = mk(cfg.dim, cfg.ffn_dim)
         self.w_up = mk(cfg.dim, cfg.ffn_dim)
         self.w_down = mk(cfg.ffn_dim, cfg.dim)
+        self._fused: Optional[_FusedColumns] = None
 
     def forward(self, x: Tensor) -> Tensor:
-        return self.w_down(F.silu(self.w_gate(x)) * self.w_up(x))
+        if self._fused is None or self._fused.layers != (self.w_gate, self.w_up):
+            self._fused = _FusedColumns(self.w_gate, self.w_up)
+        if self._fused.usable:                           # packed layers: one launch for gate and up
+            gate, up = self._fused(x)
+        else:
+            gate, up = self.w_gate(x), self.w_up(x)
+        return self.w_down(F.silu(gate) * up)
 
 
 class Block(nn.Module):

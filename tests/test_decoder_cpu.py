@@ -125,3 +125,25 @@ def test_greedy_generation_extends_the_prompt_and_respects_the_context_limit():
     assert torch.equal(out, seq)
     with pytest.raises(ValueError, match="max_seq_len"):
         model(torch.zeros(1, 25, dtype=torch.long))
+
+
+def test_fused_sibling_layers_are_the_members_columns_side_by_side(oracle):
+    """Gate/up (and q/kv) run as one packed layer in the inference form: its buffers are the members' buffers
+    concatenated along the output columns, i.e. exactly the packed form of the concatenated weights."""
+    from bittorch_b200.nn import TernaryLinearInference
+    from bittorch_b200.utils.decoder import fuse_inference_columns
+
+    rng = np.random.default_rng(0)
+    k = 37                                                   # ragged K: 10 packed bytes per column
+    codes = [rng.integers(-1, 2, size=(n, k)).astype(np.int8) for n in (24, 9)]
+    scales = [rng.random(n).astype(np.float32) + 0.1 for n in (24, 9)]
+    layers = [TernaryLinearInference(k, c.shape[0], torch.from_numpy(oracle.pack_transposed(c)), torch.from_numpy(s),
+                                     torch.from_numpy(s * 2) if i == 1 else None)
+              for i, (c, s) in enumerate(zip(codes, scales))]
+    fused = fuse_inference_columns(layers)
+    assert fused.in_features == k and fused.out_features == 33
+    assert np.array_equal(fused.weight_packed.numpy(), oracle.pack_transposed(np.concatenate(codes, axis=0)))
+    assert np.array_equal(fused.scale.numpy(), np.concatenate(scales))
+    assert np.array_equal(fused.bias.numpy(), np.concatenate([np.zeros(24, np.float32), scales[1] * 2]))
+    with pytest.raises(ValueError, match="same input"):
+        fuse_inference_columns([layers[0], TernaryLinearInference(k + 4, 9, layers[1].weight_packed, layers[1].scale)])
