@@ -120,3 +120,23 @@ def test_missing_library_fails_loudly(tmp_path, monkeypatch):
             sys.modules["bittorch_b200._C"] = saved
         if saved_attr is not None:
             bittorch_b200._C = saved_attr
+
+
+def test_binding_stub_shown_to_reference_maintainers_matches_the_abi():
+    """The ctypes stub in INTEGRATION.md is what a maintainer of the reference would paste: it must parse, and
+    every argtypes list in it must have the arity of the real binding."""
+    import ast
+
+    from bittorch_b200 import _C
+
+    text = open(os.path.join(ROOT, "INTEGRATION.md")).read()
+    blocks = re.findall(r"```python\n(.*?)```", text, flags=re.S)
+    assert len(blocks) >= 2
+    for block in blocks:
+        ast.parse(block)
+    stub = max(blocks, key=len)
+    bound = re.findall(r"_lib\.(bt_[a-z0-9_]+)\.argtypes = \[(.*?)\]", stub)
+    assert len(bound) >= 6
+    for name, args in bound:
+        arity = len([a for a in args.split(",") if a.strip()])
+        assert arity == len(_C._SIGNATURES[name][0]), name
