@@ -1,0 +1,88 @@
+"""The private tiled layout and the tensor-core operand layout, restated in Python from the formulas in the kernel
+files' comments, checked for self-consistency on CPU: every weight of a tile has exactly one slot, the two ways the
+kernels read a tile (dp4a planes, tensor-core operand rows) see the weights the formula says they see, and the
+128-byte swizzle used for the unpacked tiles is a permutation without bank conflicts for the stores that write it."""
+
+import itertools
+
+import numpy as np
+
+
+def slot(n_local: int, k_local: int):
+    """Word index and bit shift of weight (n_local, k_local) in a 512-byte tile (csrc/retile.cuh: tile_slot)."""
+    g, qlo = n_local & 7, n_local >> 3
+    t, r = k_local >> 5, k_local & 31
+    i, qhi, j = r >> 3, (r >> 2) & 1, r & 3
+    return (4 * g + t) * 4 + (qlo | (qhi << 1)), 8 * j + 2 * i
+
+
+def test_every_weight_of_a_tile_has_exactly_one_two_bit_slot():
+    seen = set()
+    for n, k in itertools.product(range(16), range(128)):
+        word, shift = slot(n, k)
+        assert 0 <= word < 128 and shift in range(0, 32, 2)
+        seen.add((word, shift))
+    assert len(seen) == 16 * 128                      # 128 words x 16 fields, all used once
+
+
+def _tile_words(codes):
+    """codes: int array [16, 128] in {-1,0,1} -> the tile's 128 32-bit words (weights stored as t + 1)."""
+    words = np.zeros(128, dtype=np.uint64)
+    for n, k in itertools.product(range(16), range(128)):
+        word, shift = slot(n, k)
+        words[word] |= np.uint64(int(codes[n, k]) + 1) << np.uint64(shift)
+    return words.astype(np.uint32)
+
+
+def test_a_masked_plane_is_four_consecutive_inputs_of_one_column():
+    """Decode kernel: lane 4g+t, word q, plane i -> bytes (t+1) * 4^i of column g + 8(q&1),
+    inputs 32t + 8i + 4(q>>1) + 0..3."""
+    rng = np.random.default_rng(0)
+    codes = rng.integers(-1, 2, size=(16, 128))
+    words = _tile_words(codes)
+    for lane, q, i in itertools.product(range(32), range(4), range(4)):
+        g, t = lane >> 2, lane & 3
+        w = int(words[lane * 4 + q])
+        plane = (w >> (2 * i)) & 0x03030303
+        n = g + 8 * (q & 1)
+        k0 = 32 * t + 8 * i + 4 * (q >> 1)
+        got = [((plane >> (8 * j)) & 0xFF) - 1 for j in range(4)]
+        assert got == [int(codes[n, k0 + j]) for j in range(4)]
+
+
+def test_unpacked_operand_rows_and_swizzle():
+    """Tensor-core kernels: lane (g,t) writes, for column g + 8h, chunk 2t + c (16 bytes = inputs 32t + 16c + 0..15,
+    planes 2c and 2c+1 of the words h and h+2) of a K-major 128-byte row, at chunk position (2t + c) ^ (row & 7).
+    Read back through the same swizzle, row n must be inputs 0..127 of column n in order."""
+    rng = np.random.default_rng(1)
+    codes = rng.integers(-1, 2, size=(16, 128))
+    words = _tile_words(codes).reshape(32, 4)
+    smem = np.full((16, 128), 255, dtype=np.uint8)           # 16 rows x 128 bytes (two 8-row swizzle atoms)
+    for lane in range(32):
+        g, t = lane >> 2, lane & 3
+        w = [int(x) for x in words[lane]]
+        for h in range(2):
+            row = g + 8 * h
+            for c in range(2):
+                v = [(w[h] >> (4 * c)) & 0x03030303, (w[h + 2] >> (4 * c)) & 0x03030303,
+                     (w[h] >> (4 * c + 2)) & 0x03030303, (w[h + 2] >> (4 * c + 2)) & 0x03030303]
+                chunk = ((2 * t + c) ^ (row & 7)) * 16
+                for wi, word in enumerate(v):
+                    for b in range(4):
+                        smem[row, chunk + 4 * wi + b] = (word >> (8 * b)) & 0xFF
+    assert smem.max() <= 2                                   # every byte written
+    for n in range(16):
+        row = np.concatenate([smem[n, ((c ^ (n & 7)) * 16):((c ^ (n & 7)) * 16 + 16)] for c in range(8)])
+        assert np.array_equal(row.astype(np.int64) - 1, codes[n])
+
+
+def test_the_stores_of_a_quarter_warp_touch_every_bank_once():
+    """A 16-byte store is issued per quarter warp (8 lanes = 2 values of g x 4 values of t): the eight chunks must
+    fall into eight different 16-byte bank groups of the 128-byte row."""
+    for h, c, quarter in itertools.product(range(2), range(2), range(4)):
+        groups = set()
+        for lane in range(8 * quarter, 8 * quarter + 8):
+            g, t = lane >> 2, lane & 3
+            row = g + 8 * h
+            groups.add((2 * t + c) ^ (row & 7))              # rows are 128 bytes apart: same banks, chunk decides
+        assert len(groups) == 8
