@@ -86,3 +86,34 @@ def test_the_stores_of_a_quarter_warp_touch_every_bank_once():
             row = g + 8 * h
             groups.add((2 * t + c) ^ (row & 7))              # rows are 128 bytes apart: same banks, chunk decides
         assert len(groups) == 8
+
+
+def test_plane_arithmetic_of_the_decode_kernel_is_exact():
+    """Decode kernel: planes 0..2 enter dp4a as unsigned codes (t+1) * 4^i, plane 3 as the signed bytes
+    (field ^ 0x40) = -t * 64; the fold acc0 + (acc1 >> 2) + (acc2 >> 4) - (acc3 >> 6) minus the activation sum over
+    the inputs that met planes 0..2 must be the plain ternary dot product (arithmetic shifts of exact multiples)."""
+    rng = np.random.default_rng(2)
+    for _ in range(50):
+        t = rng.integers(-1, 2, size=(4, 64))                 # plane i, 64 weights each
+        x = rng.integers(-127, 128, size=(4, 64))
+        acc = []
+        for i in range(3):
+            acc.append(int(((t[i] + 1) * 4 ** i * x[i]).sum()))
+        field = (t[3] + 1) << 6                                # 0x00, 0x40, 0x80 in the top two bits
+        signed = ((field ^ 0x40) + 128) % 256 - 128            # as signed bytes: +64, 0, -64
+        assert set(np.unique(signed)).issubset({64, 0, -64}) and np.array_equal(signed, -t[3] * 64)
+        acc.append(int((signed * x[3]).sum()))
+        folded = acc[0] + (acc[1] >> 2) + (acc[2] >> 4) - (acc[3] >> 6)
+        want = int((t * x).sum())
+        assert folded - int(x[:3].sum()) == want
+
+
+def test_row_sum_correction_of_the_tensor_core_kernels_is_exact():
+    """GEMM kernels multiply u8 codes t + 1 and subtract the int8 row sum: sum((t+1) x) - sum(x) = sum(t x), and
+    128 * 127 * K stays inside int32 for the largest supported K."""
+    rng = np.random.default_rng(3)
+    t = rng.integers(-1, 2, size=(5, 777))
+    x = rng.integers(-127, 128, size=(3, 777))
+    acc = x @ (t + 1).T - x.sum(axis=1, keepdims=True)
+    assert np.array_equal(acc, x @ t.T)
+    assert 2 * 127 * 131072 < 2 ** 31                          # worst accumulator before the correction
