@@ -117,3 +117,23 @@ def test_row_sum_correction_of_the_tensor_core_kernels_is_exact():
     acc = x @ (t + 1).T - x.sum(axis=1, keepdims=True)
     assert np.array_equal(acc, x @ t.T)
     assert 2 * 127 * 131072 < 2 ** 31                          # worst accumulator before the correction
+
+
+def test_k_split_of_the_narrow_batch_gemm_covers_every_block_once():
+    """Narrow-batch GEMM: CTA r of a cluster of s contracts K blocks [r*KB/s, (r+1)*KB/s) and finishes columns
+    [r*256/s, (r+1)*256/s) of the tile; every 32-column chunk of an accumulator goes to exactly one owner."""
+    for kb_total in (1, 2, 3, 8, 31, 32, 86, 224):
+        for s in (2, 4, 8):
+            if s > kb_total:
+                continue
+            covered = []
+            for r in range(s):
+                lo, hi = r * kb_total // s, (r + 1) * kb_total // s
+                assert hi > lo                                   # no idle CTA when s <= number of blocks
+                covered += list(range(lo, hi))
+            assert covered == list(range(kb_total))
+    for s in (2, 4, 8):
+        cols_own = 256 // s
+        owners = [(c0 // cols_own, c0 % cols_own) for c0 in range(0, 256, 32)]
+        assert sorted(set(o for o, _ in owners)) == list(range(s))
+        assert all(off + 32 <= cols_own for _, off in owners)
