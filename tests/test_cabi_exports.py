@@ -126,6 +126,7 @@ def test_binding_stub_shown_to_reference_maintainers_matches_the_abi():
     """The ctypes stub in INTEGRATION.md is what a maintainer of the reference would paste: it must parse, and
     every argtypes list in it must have the arity of the real binding."""
     import ast
+    import textwrap
 
     from bittorch_b200 import _C
 
@@ -133,7 +134,7 @@ def test_binding_stub_shown_to_reference_maintainers_matches_the_abi():
     blocks = re.findall(r"```python\n(.*?)```", text, flags=re.S)
     assert len(blocks) >= 2
     for block in blocks:
-        ast.parse(block)
+        ast.parse(textwrap.dedent(block))
     stub = max(blocks, key=len)
     bound = re.findall(r"_lib\.(bt_[a-z0-9_]+)\.argtypes = \[(.*?)\]", stub)
     assert len(bound) >= 6
