@@ -19,6 +19,12 @@ prompt, then one token at a time against a key/value cache):
 
 The layers are built as ``TernaryLinear`` (trainable masters; ``backend="python"`` runs anywhere);
 ``to_inference()`` swaps them for packed ``TernaryLinearInference`` layers on a CUDA device.
+
+Two ways to run a single-token step: ``forward(tokens, cache, pos0)`` with the position as a Python integer
+(shapes grow with the position), and ``decode_step(tokens, cache, pos)`` with the position in a device tensor and
+every shape fixed (attention runs over the whole cache under a mask), which is what a CUDA graph can replay:
+``GreedyDecodeGraph`` captures one such step, the arg-max and the position increment, so that a decoded token
+costs one graph launch and no host synchronisation.
 """
 
 from __future__ import annotations
@@ -92,6 +98,15 @@ def apply_rope(x: Tensor, cos: Tensor, sin: Tensor, pos0: int) -> Tensor:
     return torch.cat([x0 * c - x1 * s, x0 * s + x1 * c], dim=-1)
 
 
+def apply_rope_at(x: Tensor, cos: Tensor, sin: Tensor, pos: Tensor) -> Tensor:
+    """x: [B, H, 1, head_dim]; as ``apply_rope`` for the single position held in the device tensor ``pos`` [1]."""
+    half = x.shape[3] // 2
+    c = cos.index_select(0, pos)[None, None].to(x.dtype)             # [1, 1, 1, half]
+    s = sin.index_select(0, pos)[None, None].to(x.dtype)
+    x0, x1 = x[..., :half], x[..., half:]
+    return torch.cat([x0 * c - x1 * s, x0 * s + x1 * c], dim=-1)
+
+
 def fuse_inference_columns(layers) -> TernaryLinearInference:
     """Packed layers that read the same input, as ONE layer with their output columns side by side.  Columns of a
     packed ternary layer are independent (own bytes, own scale; the activation quantizer depends on the input
@@ -141,7 +156,8 @@ class Attention(nn.Module):
         self.proj = mk(cfg.dim, cfg.dim)
         self._fused: Optional[_FusedColumns] = None
 
-    def forward(self, x: Tensor, cache: Tuple[Tensor, Tensor], pos0: int, cos: Tensor, sin: Tensor) -> Tensor:
+    def _qkv(self, x: Tensor):
+        """x [B, T, dim] -> q [B, H, T, hd], k and v [B, Hkv, T, hd] (not yet rotated)."""
         cfg = self.cfg
         b, t, _ = x.shape
         hd, nh, nkv = cfg.head_dim, cfg.n_heads, cfg.n_kv_heads
@@ -151,10 +167,15 @@ class Attention(nn.Module):
             q, kv = self._fused(x)
         else:
             q, kv = self.q_proj(x), self.kv_proj(x)
-        q = q.reshape(b, t, nh, hd).transpose(1, 2)                              # [B, H, T, hd]
+        q = q.reshape(b, t, nh, hd).transpose(1, 2)
         kv = kv.reshape(b, t, 2, nkv, hd)
-        k = kv[:, :, 0].transpose(1, 2)                                          # [B, Hkv, T, hd]
-        v = kv[:, :, 1].transpose(1, 2)
+        return q, kv[:, :, 0].transpose(1, 2), kv[:, :, 1].transpose(1, 2)
+
+    def forward(self, x: Tensor, cache: Tuple[Tensor, Tensor], pos0: int, cos: Tensor, sin: Tensor) -> Tensor:
+        cfg = self.cfg
+        b, t, _ = x.shape
+        hd, nh, nkv = cfg.head_dim, cfg.n_heads, cfg.n_kv_heads
+        q, k, v = self._qkv(x)
         q = apply_rope(q, cos, sin, pos0)
         k_cache, v_cache = cache                                                 # [B, Hkv, max_seq_len, hd]
         k_cache[:, :, pos0:pos0 + t] = apply_rope(k, cos, sin, pos0).to(k_cache.dtype)   # keys are stored rotated
@@ -168,6 +189,28 @@ class Attention(nn.Module):
         mask = torch.ones(t, pos0 + t, dtype=torch.bool, device=x.device).tril(diagonal=pos0)
         out = F.scaled_dot_product_attention(q, keys, vals, attn_mask=mask, scale=1.0 / math.sqrt(hd))
         return self.proj(out.transpose(1, 2).reshape(b, t, cfg.dim))
+
+    def decode_step(self, x: Tensor, cache: Tuple[Tensor, Tensor], pos: Tensor, cos: Tensor, sin: Tensor) -> Tensor:
+        """One token per sequence at the position in the device tensor ``pos`` [1] (int64): x [B, 1, dim].  Every
+        shape is independent of the position: the new key/value go into the cache with ``index_copy_`` and the
+        query attends over the WHOLE cache with the positions after ``pos`` masked out.  The query heads of one
+        key/value head are batched against it ([B, Hkv, group, hd] x [B, Hkv, S, hd]), so grouped-query attention
+        copies nothing."""
+        cfg = self.cfg
+        b = x.shape[0]
+        hd, nh, nkv = cfg.head_dim, cfg.n_heads, cfg.n_kv_heads
+        q, k, v = self._qkv(x)
+        q = apply_rope_at(q, cos, sin, pos)
+        k_cache, v_cache = cache
+        k_cache.index_copy_(2, pos, apply_rope_at(k, cos, sin, pos).to(k_cache.dtype))
+        v_cache.index_copy_(2, pos, v.to(v_cache.dtype))
+        seq = k_cache.shape[2]
+        qg = q.reshape(b, nkv, nh // nkv, hd)                                    # query head h = kv head * group + g
+        scores = torch.matmul(qg, k_cache.to(q.dtype).transpose(2, 3)) * (1.0 / math.sqrt(hd))     # [B, Hkv, group, S]
+        visible = torch.arange(seq, device=x.device) <= pos                      # [S]
+        scores = scores.float().masked_fill(~visible, float("-inf"))
+        out = torch.matmul(torch.softmax(scores, dim=-1).to(q.dtype), v_cache.to(q.dtype))          # [B, Hkv, group, hd]
+        return self.proj(out.reshape(b, 1, cfg.dim))
 
 
 class SwiGLU(nn.Module):
@@ -199,6 +242,10 @@ class Block(nn.Module):
 
     def forward(self, x: Tensor, cache, pos0: int, cos: Tensor, sin: Tensor) -> Tensor:
         x = x + self.attn(self.norm1(x), cache, pos0, cos, sin)
+        return x + self.mlp(self.norm2(x))
+
+    def decode_step(self, x: Tensor, cache, pos: Tensor, cos: Tensor, sin: Tensor) -> Tensor:
+        x = x + self.attn.decode_step(self.norm1(x), cache, pos, cos, sin)
         return x + self.mlp(self.norm2(x))
 
 
@@ -238,6 +285,14 @@ class TernaryDecoder(nn.Module):
             x = block(x, layer_cache, pos0, self.rope_cos, self.rope_sin)
         return self.head(self.norm(x))
 
+    def decode_step(self, tokens: Tensor, cache: list, pos: Tensor) -> Tensor:
+        """tokens [B, 1] at the position held in the device tensor ``pos`` [1] (int64) -> logits [B, 1, vocab].
+        Same result as ``forward(tokens, cache, int(pos))``, with shapes that do not depend on the position."""
+        x = self.tok(tokens)
+        for block, layer_cache in zip(self.blocks, cache):
+            x = block.decode_step(x, layer_cache, pos, self.rope_cos, self.rope_sin)
+        return self.head(self.norm(x))
+
     @torch.no_grad()
     def generate_greedy(self, prompt: Tensor, new_tokens: int) -> Tensor:
         """Prefill over ``prompt`` [B, T], then ``new_tokens`` greedy steps against the cache -> [B, T + new_tokens]."""
@@ -258,3 +313,74 @@ class TernaryDecoder(nn.Module):
 
         convert_linear_layers(self, skip_names=["head"], inplace=True)
         return self
+
+
+class GreedyDecodeGraph:
+    """Greedy decoding with one CUDA-graph launch per token.
+
+    The captured step reads the current tokens [B, 1] and the position from device buffers, runs
+    ``TernaryDecoder.decode_step``, writes the arg-max back into the token buffer and advances the position, so
+    consecutive replays decode consecutive tokens without the host looking at any result.  ``history`` [B,
+    max_seq_len] receives every token at its position.  The model must be in its inference form on a CUDA device.
+    """
+
+    def __init__(self, model: TernaryDecoder, batch: int, cache: Optional[list] = None, capture=None) -> None:
+        self.model = model
+        dev = model.tok.weight.device
+        self.cache = cache if cache is not None else model.new_cache(batch)
+        self.tokens = torch.zeros((batch, 1), dtype=torch.long, device=dev)
+        self.pos = torch.zeros((1,), dtype=torch.long, device=dev)
+        self.history = torch.zeros((batch, model.cfg.max_seq_len), dtype=torch.long, device=dev)
+        self.graph = None
+        self._host_pos = 0
+        self._capture = capture if capture is not None else _capture_cuda_graph
+
+    @torch.no_grad()
+    def _step(self) -> None:
+        self.history.index_copy_(1, self.pos, self.tokens)
+        logits = self.model.decode_step(self.tokens, self.cache, self.pos)
+        self.tokens.copy_(logits[:, -1].argmax(dim=-1, keepdim=True))
+        self.pos.add_(1)
+
+    def start(self, tokens: Tensor, pos0: int) -> None:
+        """Set the tokens [B, 1] to feed next and their position; captures the graph on first use.  The capture's
+        warm-up calls run the step at ``pos0`` itself (they write scratch keys/values into that one cache slot, which
+        the first real step overwrites before anything reads it)."""
+        if not (0 <= pos0 < self.model.cfg.max_seq_len):
+            raise ValueError(f"position {pos0} is outside the cache (max_seq_len={self.model.cfg.max_seq_len})")
+
+        def reset() -> None:
+            self.tokens.copy_(tokens)
+            self.pos.fill_(pos0)
+
+        reset()
+        if self.graph is None:
+            self.graph = self._capture(self._step, reset)
+        self._host_pos = pos0
+
+    def run(self, steps: int) -> None:
+        """Decode ``steps`` tokens: ``steps`` graph launches, nothing else."""
+        if self.graph is None:
+            raise RuntimeError("call start() first")
+        if self._host_pos + steps > self.model.cfg.max_seq_len:
+            raise ValueError(f"{steps} steps from position {self._host_pos} exceed max_seq_len={self.model.cfg.max_seq_len}")
+        for _ in range(steps):
+            self.graph.replay()
+        self._host_pos += steps
+
+
+def _capture_cuda_graph(step_fn, reset, warm: int = 3):
+    """Runs ``step_fn`` a few times on a side stream (first calls build caches and must not be captured), calling
+    ``reset`` after each, then captures one call into a CUDA graph."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(warm):
+            step_fn()
+            reset()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        step_fn()
+    return graph

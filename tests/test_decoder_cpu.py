@@ -147,3 +147,55 @@ def test_fused_sibling_layers_are_the_members_columns_side_by_side(oracle):
     assert np.array_equal(fused.bias.numpy(), np.concatenate([np.zeros(24, np.float32), scales[1] * 2]))
     with pytest.raises(ValueError, match="same input"):
         fuse_inference_columns([layers[0], TernaryLinearInference(k + 4, 9, layers[1].weight_packed, layers[1].scale)])
+
+
+@pytest.mark.parametrize("n_kv_heads", [4, 2, 1])
+def test_fixed_shape_decode_step_equals_the_growing_shape_step(n_kv_heads):
+    """decode_step (position in a tensor, attention over the whole cache under a mask) against forward (position as
+    an integer, attention over the filled part): same logits and same cache contents (to float tolerance: the attention arithmetic differs), step after step."""
+    torch.manual_seed(3)
+    model = TernaryDecoder(_cfg(n_kv_heads=n_kv_heads)).eval()
+    tokens = torch.randint(0, 65, (2, 9))
+    with torch.no_grad():
+        cache_a, cache_b = model.new_cache(2), model.new_cache(2)
+        model(tokens[:, :5], cache_a, 0)
+        model(tokens[:, :5], cache_b, 0)
+        for i in range(5, 9):
+            want = model(tokens[:, i:i + 1], cache_a, i)
+            got = model.decode_step(tokens[:, i:i + 1], cache_b, torch.tensor([i]))
+            assert torch.allclose(got, want, atol=1e-5)
+        for (ka, va), (kb, vb) in zip(cache_a, cache_b):
+            assert torch.allclose(ka, kb, atol=1e-5) and torch.allclose(va, vb, atol=1e-5)   # two softmax codes upstream
+
+
+def test_greedy_decode_graph_produces_generate_greedys_tokens():
+    """GreedyDecodeGraph with the capture replaced by a plain callable (no GPU here): the device-side loop (token
+    buffer, position counter, history) yields the tokens of generate_greedy."""
+    from bittorch_b200.utils.decoder import GreedyDecodeGraph
+
+    class Replayable:
+        def __init__(self, fn):
+            self.fn = fn
+
+        def replay(self):
+            self.fn()
+
+    def capture(step_fn, reset):
+        for _ in range(3):                                    # like the real capture: warm-up calls, each undone
+            step_fn()
+            reset()
+        return Replayable(step_fn)
+
+    torch.manual_seed(4)
+    model = TernaryDecoder(_cfg()).eval()
+    prompt = torch.randint(0, 65, (3, 4))
+    want = model.generate_greedy(prompt, 8)
+    with torch.no_grad():
+        cache = model.new_cache(3)
+        first = model(prompt, cache, 0)[:, -1].argmax(dim=-1, keepdim=True)
+    loop = GreedyDecodeGraph(model, 3, cache=cache, capture=capture)
+    loop.start(first, 4)
+    loop.run(8)
+    assert torch.equal(loop.history[:, 4:12], want[:, 4:12])
+    with pytest.raises(ValueError):
+        loop.run(24)
