@@ -356,6 +356,7 @@ class GreedyDecodeGraph:
         reset()
         if self.graph is None:
             self.graph = self._capture(self._step, reset)
+            reset()
         self._host_pos = pos0
 
     def run(self, steps: int) -> None:

@@ -202,10 +202,11 @@ def packed_forward_i8_threaded(x, packed_t, k: int, scale, bias=None, threads: i
 def ref_python_forward(x, weight, bias=None, threshold_factor: float = 0.05):
     """Eager-torch restatement of the reference's CPU "python backend" forward.
 
-    Follows bittorch/nn/ternary_linear.py:196-213 and bittorch/quant/ternary.py:122-142:
-    re-quantize the full-precision master weight on every call, build the effective
-    weight ``T * scale`` in the input dtype and run a dense ``F.linear``.  Takes and
-    returns torch CPU tensors; used as the timed CPU baseline next to the GPU numbers.
+    Follows bittorch/nn/ternary_linear.py:196-213 and bittorch/quant/ternary.py:122-142,189: re-quantize the
+    full-precision master weight on every call, apply the straight-through rewrite ``T.detach() - W.detach() + W``
+    (two more passes over the weight, which the reference executes in inference too), build the effective weight
+    ``w_q * scale`` in the input dtype and run a dense ``F.linear``.  Takes and returns torch CPU tensors; used as
+    the timed CPU baseline next to the GPU numbers.
     """
     import torch
     import torch.nn.functional as F
@@ -215,6 +216,7 @@ def ref_python_forward(x, weight, bias=None, threshold_factor: float = 0.05):
         scale = absw.max(dim=1, keepdim=True).values.clamp(min=1e-8)
         thr = threshold_factor * scale
         t = torch.where(absw > thr, torch.sign(weight), torch.zeros_like(weight))
-        w_eff = (t * scale).to(x.dtype)
+        w_q = t.detach() - weight.detach() + weight            # quant/ternary.py:189
+        w_eff = (w_q * scale).to(x.dtype)
         b = None if bias is None else bias.to(x.dtype)
         return F.linear(x, w_eff, b)
