@@ -330,7 +330,7 @@ def launch_linear(layer: Layer, m: int, x: torch.Tensor, ldx: int, y: torch.Tens
     if m <= _C.DECODE_MAX_M:
         _C._check(lib.bt_gemv_tiled(x.data_ptr(), _C.BT_BF16, m, layer.k, ldx, layer.tiled.data_ptr(), layer.n_local,
                                     layer.scale.data_ptr(), None, y.data_ptr(), _C.BT_BF16, y.stride(0),
-                                    None, None, None, st))
+                                    None, None, None, _C.LAUNCH_DEFAULT, st))
         return 1
     xq, sx, xsum = scratch
     _C._check(lib.bt_act_quant_i8(x.data_ptr(), _C.BT_BF16, m, layer.k, ldx, xq.data_ptr(), sx.data_ptr(),

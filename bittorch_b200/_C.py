@@ -20,10 +20,14 @@ from torch import Tensor
 
 from . import _build
 
-BT_F32, BT_F16, BT_BF16 = 0, 1, 2
+BT_F32, BT_F16, BT_BF16, BT_F64 = 0, 1, 2, 3
+LAUNCH_DEFAULT, LAUNCH_WEIGHTS_JUST_WRITTEN = 0, 1
+TUNE_GEMM_PAIR, TUNE_GEMM_BN, TUNE_GEMM_SPLIT, TUNE_GEMV_SPLIT = 0, 1, 2, 3
 GEMV_MAX_M = 16          # largest batch the decode kernels accept
 DECODE_MAX_M = 4         # batches up to here run the decode kernel; above it the tensor-core kernel is faster
 _DT = {torch.float32: BT_F32, torch.float16: BT_F16, torch.bfloat16: BT_BF16}
+_DT_FLOAT_PATH = dict(_DT)
+_DT_FLOAT_PATH[torch.float64] = BT_F64     # the floating-point-activation entry points also take float64
 
 _p = ctypes.c_void_p
 _i64 = ctypes.c_int64
@@ -34,17 +38,21 @@ _SIGNATURES = {
     "bt_version": ([], _int),
     "bt_last_error": ([], ctypes.c_char_p),
     "bt_device_status": ([_p, _p], _int),
+    "bt_set_tuning": ([_int, _int], _int),
+    "bt_selftest_wait_timeout": ([_p], _int),
     "bt_dummy": ([_p, _p, ctypes.c_size_t, _p], _int),
     "bt_quantize_pack": ([_p, _int, _i64, _i64, _i64, _f32, _p, _p, _p, _p, _p], _int),
     "bt_pack_codes": ([_p, _i64, _i64, _p, _p], _int),
     "bt_unpack_codes": ([_p, _i64, _i64, _p, _p], _int),
+    "bt_pack_codes_rows": ([_p, _i64, _i64, _p, _p], _int),
+    "bt_unpack_codes_rows": ([_p, _i64, _i64, _p, _p], _int),
     "bt_act_quant_i8": ([_p, _int, _i64, _i64, _i64, _p, _p, _p, _p], _int),
     "bt_tiled_bytes": ([_i64, _i64], ctypes.c_size_t),
     "bt_retile_packed": ([_p, _i64, _i64, _p, _p], _int),
     "bt_untile_packed": ([_p, _i64, _i64, _p, _p], _int),
     "bt_gemv_packed_i8": ([_p, _p, _i64, _i64, _p, _i64, _p, _p, _p, _int, _i64, _p, _p], _int),
-    "bt_gemv_tiled_i8": ([_p, _p, _i64, _i64, _p, _i64, _p, _p, _p, _int, _i64, _p, _p], _int),
-    "bt_gemv_tiled": ([_p, _int, _i64, _i64, _i64, _p, _i64, _p, _p, _p, _int, _i64, _p, _p, _p, _p], _int),
+    "bt_gemv_tiled_i8": ([_p, _p, _i64, _i64, _p, _i64, _p, _p, _p, _int, _i64, _p, _int, _p], _int),
+    "bt_gemv_tiled": ([_p, _int, _i64, _i64, _i64, _p, _i64, _p, _p, _p, _int, _i64, _p, _p, _p, _int, _p], _int),
     "bt_gemm_tiled_i8": ([_p, _p, _p, _i64, _i64, _p, _i64, _p, _p, _p, _int, _i64, _p, _p], _int),
     "bt_linear_unpacked": ([_p, _int, _i64, _i64, _p, _i64, _p, _p, _p, _p], _int),
     "bt_linear_packed_float": ([_p, _int, _i64, _i64, _p, _i64, _p, _p, _p, _p], _int),
@@ -55,8 +63,7 @@ def _load() -> ctypes.CDLL:
     path = os.environ.get("BITTORCH_B200_LIB", _build.LIB_PATH)
     if not os.path.exists(path):
         raise ImportError(
-            f"bittorch_b200: {path} has not been built; run `python -c 'import __graft_entry__ as g; g.build()'` "
-            "or `python -m bittorch_b200._build`"
+            f"bittorch_b200: {path} has not been built; run `python -m bittorch_b200._build`"
         )
     try:
         lib = ctypes.CDLL(path)
@@ -95,11 +102,12 @@ def _stream(t: Tensor):
     return torch.cuda.current_stream(t.device).cuda_stream
 
 
-def _dtype_code(t: Tensor, what: str) -> int:
+def _dtype_code(t: Tensor, what: str, float_path: bool = False) -> int:
     try:
-        return _DT[t.dtype]
+        return (_DT_FLOAT_PATH if float_path else _DT)[t.dtype]
     except KeyError:
-        raise RuntimeError(f"{what} must be float32, float16 or bfloat16, got {t.dtype}") from None
+        raise RuntimeError(f"{what} must be float32, float16 or bfloat16"
+                           f"{' or float64' if float_path else ''}, got {t.dtype}") from None
 
 
 def _f32vec(t: Optional[Tensor]) -> Optional[Tensor]:
@@ -107,6 +115,18 @@ def _f32vec(t: Optional[Tensor]) -> Optional[Tensor]:
     if t is None:
         return None
     return t.detach().to(torch.float32).contiguous()
+
+
+def set_tuning(knob: int, value: int) -> None:
+    """Kernel-selection override for tests and tuning (``TUNE_*``); -1 = automatic.  Process-wide."""
+    _check(_lib.bt_set_tuning(int(knob), int(value)))
+
+
+def selftest_wait_timeout(device=None) -> None:
+    """Enqueues the library's wait-timeout self-test kernel; ``device_status`` then reads 4 once."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    with torch.cuda.device(dev):
+        _check(_lib.bt_selftest_wait_timeout(torch.cuda.current_stream(dev).cuda_stream))
 
 
 def device_status(device=None) -> int:
@@ -175,6 +195,28 @@ def pack_codes(codes: Tensor) -> Tensor:
     return out
 
 
+def pack_codes_rows(codes: Tensor) -> Tensor:
+    """int8 codes [N,K] -> packed uint8 [N, ceil(K/4)] (the row layout of ``pack_ternary``)."""
+    _require_cuda(codes)
+    codes = codes.contiguous()
+    n, k = codes.shape
+    out = torch.empty((n, (k + 3) // 4), dtype=torch.uint8, device=codes.device)
+    with torch.cuda.device(codes.device):
+        _check(_lib.bt_pack_codes_rows(_ptr(codes), n, k, _ptr(out), _stream(codes)))
+    return out
+
+
+def unpack_codes_rows(packed: Tensor, in_features: int) -> Tensor:
+    """packed uint8 [N, ceil(K/4)] -> int8 codes [N,K]."""
+    _require_cuda(packed)
+    packed = packed.contiguous()
+    n = packed.shape[0]
+    out = torch.empty((n, in_features), dtype=torch.int8, device=packed.device)
+    with torch.cuda.device(packed.device):
+        _check(_lib.bt_unpack_codes_rows(_ptr(packed), n, in_features, _ptr(out), _stream(packed)))
+    return out
+
+
 def unpack_codes(packed_T: Tensor, in_features: int) -> Tensor:
     """public packed uint8 [ceil(K/4), N] -> int8 codes [N,K]."""
     _require_cuda(packed_T)
@@ -227,13 +269,14 @@ def untile(tiled: Tensor, in_features: int, out_features: int) -> Tensor:
 
 
 def _int_linear(fn, xq: Tensor, sx: Tensor, w: Tensor, k: int, n: int, scale: Tensor, bias: Optional[Tensor],
-                out_dtype: torch.dtype, want_acc: bool, out: Optional[Tensor] = None):
+                out_dtype: torch.dtype, want_acc: bool, out: Optional[Tensor] = None, flags: Optional[int] = None):
     m = xq.shape[0]
     y = torch.empty((m, n), dtype=out_dtype, device=xq.device) if out is None else out
     acc = torch.empty((m, n), dtype=torch.int32, device=xq.device) if want_acc else None
+    extra = () if flags is None else (int(flags),)
     with torch.cuda.device(xq.device):
         _check(fn(_ptr(xq), _ptr(sx), m, k, _ptr(w), n, _ptr(scale), _ptr(bias), _ptr(y), _DT[out_dtype], y.stride(0),
-                  _ptr(acc), _stream(xq)))
+                  _ptr(acc), *extra, _stream(xq)))
     return (y, acc) if want_acc else y
 
 
@@ -244,17 +287,22 @@ def gemv_packed_i8(xq, sx, packed_T, in_features, scale, bias=None, out_dtype=to
 
 
 def gemv_tiled_i8(xq, sx, tiled, in_features, out_features, scale, bias=None, out_dtype=torch.float32, want_acc=False,
-                  out=None):
-    """Decode-size integer linear on the tiled layout (M <= 16): the bandwidth-bound fast path."""
+                  out=None, fresh_weights: bool = False):
+    """Decode-size integer linear on the tiled layout (M <= 16): the bandwidth-bound fast path.
+
+    ``fresh_weights``: ``tiled`` / ``scale`` / ``bias`` were written by work enqueued just before this call on the
+    same stream; the kernel is then launched fully stream-ordered instead of overlapping its predecessor."""
     return _int_linear(_lib.bt_gemv_tiled_i8, xq, sx, tiled, in_features, out_features, scale, bias, out_dtype,
-                       want_acc, out)
+                       want_acc, out, flags=LAUNCH_WEIGHTS_JUST_WRITTEN if fresh_weights else LAUNCH_DEFAULT)
 
 
 def gemv_tiled(x2d: Tensor, tiled: Tensor, in_features: int, out_features: int, scale: Tensor,
-               bias: Optional[Tensor] = None, out: Optional[Tensor] = None, want_debug: bool = False):
+               bias: Optional[Tensor] = None, out: Optional[Tensor] = None, want_debug: bool = False,
+               fresh_weights: bool = False):
     """Decode-size linear from floating-point activations in one kernel (fused int8 quantizer).
 
     ``want_debug`` also returns the int8 activations, their scales and the int32 accumulators.
+    ``fresh_weights``: see ``gemv_tiled_i8``.
     """
     if x2d.stride(1) != 1:
         x2d = x2d.contiguous()
@@ -268,7 +316,7 @@ def gemv_tiled(x2d: Tensor, tiled: Tensor, in_features: int, out_features: int, 
     with torch.cuda.device(x2d.device):
         _check(_lib.bt_gemv_tiled(_ptr(x2d), _dtype_code(x2d, "X"), m, in_features, x2d.stride(0), _ptr(tiled), out_features,
                                   _ptr(scale), _ptr(bias), _ptr(y), _DT[y.dtype], y.stride(0), _ptr(xq), _ptr(sx), _ptr(acc),
-                                  _stream(x2d)))
+                                  LAUNCH_WEIGHTS_JUST_WRITTEN if fresh_weights else LAUNCH_DEFAULT, _stream(x2d)))
     return (y, xq, sx, acc) if want_debug else y
 
 
@@ -290,7 +338,7 @@ def gemm_tiled_i8(xq, sx, tiled, in_features, out_features, scale, bias=None, ou
 
 
 def int8_linear_tiled(x2d: Tensor, tiled: Tensor, in_features: int, out_features: int, scale: Tensor,
-                      bias: Optional[Tensor]) -> Tensor:
+                      bias: Optional[Tensor], fresh_weights: bool = False) -> Tensor:
     """The integer path for any batch: one fused quantize+GEMV kernel for M <= DECODE_MAX_M
     (its dp4a arithmetic grows with M), activation quantizer + tcgen05 GEMM above (cost
     almost flat in M up to a full 128-row tile).
@@ -300,14 +348,14 @@ def int8_linear_tiled(x2d: Tensor, tiled: Tensor, in_features: int, out_features
     """
     m = x2d.shape[0]
     if m <= DECODE_MAX_M:
-        return gemv_tiled(x2d, tiled, in_features, out_features, scale, bias)
+        return gemv_tiled(x2d, tiled, in_features, out_features, scale, bias, fresh_weights=fresh_weights)
     if in_features % 16 == 0:
         xq, sx, xsum = act_quant_i8(x2d, want_sum=True)
         return gemm_tiled_i8(xq, sx, tiled, in_features, out_features, scale, bias, x2d.dtype, xsum=xsum)
     y = torch.empty((m, out_features), dtype=x2d.dtype, device=x2d.device)
     for m0 in range(0, m, GEMV_MAX_M):
         m1 = min(m, m0 + GEMV_MAX_M)
-        gemv_tiled(x2d[m0:m1], tiled, in_features, out_features, scale, bias, out=y[m0:m1])
+        gemv_tiled(x2d[m0:m1], tiled, in_features, out_features, scale, bias, out=y[m0:m1], fresh_weights=fresh_weights)
     return y
 
 
@@ -374,7 +422,7 @@ def ternary_linear_forward(X: Tensor, W_tern: Tensor, scale: Tensor, bias: Optio
     s32, b32 = _f32vec(scale), _f32vec(bias)
     y = torch.empty((x2d.shape[0], n), dtype=X.dtype, device=X.device)
     with torch.cuda.device(X.device):
-        _check(_lib.bt_linear_unpacked(_ptr(x2d), _dtype_code(x2d, "X"), x2d.shape[0], k, _ptr(w), n, _ptr(s32),
+        _check(_lib.bt_linear_unpacked(_ptr(x2d), _dtype_code(x2d, "X", float_path=True), x2d.shape[0], k, _ptr(w), n, _ptr(s32),
                                        _ptr(b32), _ptr(y), _stream(x2d)))
     return y.reshape(*X.shape[:-1], n)
 
@@ -403,16 +451,16 @@ def _packed_forward(X: Tensor, W_T: Tensor, scale: Tensor, bias: Optional[Tensor
     w = W_T.contiguous()
     s32, b32 = _f32vec(scale), _f32vec(bias)
     m = x2d.shape[0]
-    if mode == "float":
+    if mode == "float" or X.dtype == torch.float64:        # float64 exists on the float path only, as in the reference
         y = torch.empty((m, n), dtype=X.dtype, device=X.device)
         with torch.cuda.device(X.device):
-            _check(_lib.bt_linear_packed_float(_ptr(x2d), _dtype_code(x2d, "X"), m, k, _ptr(w), n, _ptr(s32), _ptr(b32),
+            _check(_lib.bt_linear_packed_float(_ptr(x2d), _dtype_code(x2d, "X", float_path=True), m, k, _ptr(w), n, _ptr(s32), _ptr(b32),
                                                _ptr(y), _stream(x2d)))
     elif m <= DECODE_MAX_M:
         xq, sx = act_quant_i8(x2d)
         y = gemv_packed_i8(xq, sx, w, k, s32, b32, X.dtype)
     else:
-        y = int8_linear_tiled(x2d, retile(w, k), k, n, s32, b32)
+        y = int8_linear_tiled(x2d, retile(w, k), k, n, s32, b32, fresh_weights=True)   # re-tiled just above
     return y.reshape(*X.shape[:-1], n)
 
 

@@ -5,6 +5,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <cstdarg>
 #include <cstdint>
 #include <cstdio>
@@ -13,9 +14,11 @@
 
 namespace bt {
 
+constexpr int BT_MAX_DEVICES = 64;
+
 // ---- host-side error plumbing --------------------------------------------------
 
-void set_error(const char* fmt, ...);   // stores a thread-local message (api.cu)
+void set_error(const char* fmt, ...);   // stores a thread-local message (lib.cu)
 
 #define BT_REQUIRE(cond, ...)                 \
     do {                                      \
@@ -58,7 +61,27 @@ __host__ __device__ inline bool aligned(const void* p, size_t a) { return (reint
 template <typename T>
 inline T ceil_div(T a, T b) { return (a + b - 1) / b; }
 
-int sm_count();   // SMs of the current device, cached (api.cu)
+int sm_count();   // SMs of the current device, cached (lib.cu)
+
+// Kernel-selection overrides for tests and tuning (lib.cu): -1 = automatic.  Set with bt_set_tuning(); the
+// environment variable of the same meaning is read once, the first time a knob is looked at.
+int tuning(int knob);
+
+// Raises a kernel's dynamic shared-memory limit once per device and size instead of on every launch.
+// `granted` is a zero-initialised per-kernel array (one slot per device ordinal).
+template <typename Kern>
+inline int ensure_dynamic_smem(Kern kern, size_t smem, std::atomic<size_t>* granted) {
+    if (smem <= 48 * 1024) return BT_OK;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= BT_MAX_DEVICES) dev = -1;
+    if (dev >= 0 && granted[dev].load(std::memory_order_acquire) >= smem) return BT_OK;
+    BT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    if (dev >= 0) {
+        size_t seen = granted[dev].load(std::memory_order_relaxed);
+        while (seen < smem && !granted[dev].compare_exchange_weak(seen, smem, std::memory_order_release)) {}
+    }
+    return BT_OK;
+}
 
 // Sticky per-device status word written by kernels whose bounded waits ran out.
 // The library is one translation unit (lib.cu includes every kernel file), so a
@@ -66,57 +89,17 @@ int sm_count();   // SMs of the current device, cached (api.cu)
 __device__ int g_device_status = 0;
 __device__ __forceinline__ void report_wait_timeout() { atomicExch(&g_device_status, BT_ERR_DEVICE_WAIT); }
 
-// Optional timeline stamps for kernel bring-up (compile with -DBT_TRACE): slot `i` of the
-// first CTA's first thread receives the global nanosecond timer.  Compiled out otherwise.
-#ifdef BT_TRACE
-__device__ unsigned long long g_trace[128];
-__device__ __forceinline__ void bt_stamp(int i) {
-    if (blockIdx.x == 0 && blockIdx.y == 0 && (threadIdx.x & 31) == 0) {
-        unsigned long long t;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-        if (threadIdx.x == 0) g_trace[i] = t;
-    }
-}
-#define BT_STAMP(i) ::bt::bt_stamp(i)
-// per-warp stamp of CTA 0: slot 32 + warp
-__device__ __forceinline__ void bt_stamp_warp(int base) {
-    if (blockIdx.x == 0 && blockIdx.y == 0 && (threadIdx.x & 31) == 0) {
-        unsigned long long t;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-        g_trace[base + (threadIdx.x >> 5)] = t;
-    }
-}
-#define BT_STAMP_WARP(b) ::bt::bt_stamp_warp(b)
-// per-CTA stamps: slot j (0..3) of every CTA (linear block index)
-__device__ unsigned long long g_trace_cta[4096 * 4];
-__device__ unsigned int g_trace_sm[4096];
-__device__ __forceinline__ void bt_stamp_cta(int j) {
-    const unsigned id = blockIdx.x + gridDim.x * blockIdx.y;
-    if (id < 4096 && threadIdx.x == 0) {
-        unsigned long long t;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-        g_trace_cta[id * 4 + j] = t;
-        unsigned int smid;
-        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-        g_trace_sm[id] = smid;
-    }
-}
-#define BT_STAMP_CTA(j) ::bt::bt_stamp_cta(j)
-#else
-#define BT_STAMP(i) ((void)0)
-#define BT_STAMP_CTA(j) ((void)0)
-#define BT_STAMP_WARP(b) ((void)0)
-#endif
-
 // ---- device helpers --------------------------------------------------------------
 
 template <typename T> __device__ __forceinline__ float to_float(T v);
 template <> __device__ __forceinline__ float to_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_float<double>(double v) { return static_cast<float>(v); }
 template <> __device__ __forceinline__ float to_float<__half>(__half v) { return __half2float(v); }
 template <> __device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
 
 template <typename T> __device__ __forceinline__ T from_float(float v);
 template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ double from_float<double>(float v) { return static_cast<double>(v); }
 template <> __device__ __forceinline__ __half from_float<__half>(float v) { return __float2half_rn(v); }
 template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 
@@ -279,14 +262,6 @@ __device__ __forceinline__ int ld_dsmem_s32(const void* local_smem_ptr, uint32_t
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(local_smem_ptr)), "r"(cta_rank));
     asm volatile("ld.shared::cluster.s32 %0, [%1];" : "=r"(v) : "r"(remote) : "memory");
     return v;
-}
-
-// Legacy warp-level int8 MMA, unsigned A (weight codes) x signed B (activations).
-__device__ __forceinline__ void mma_u8s8_16x8x32(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
 }  // namespace bt

@@ -23,6 +23,8 @@
 
 #include <cuda.h>   // CUtensorMap types only; the encoder is looked up at run time
 
+#include <mutex>
+
 #include "common.cuh"
 #include "retile.cuh"
 
@@ -259,6 +261,9 @@ __device__ __forceinline__ uint32_t map_to_cta(const void* local_smem_ptr, uint3
 }
 __device__ __forceinline__ void st_cluster_v4(uint32_t cluster_addr, int a, int b, int c, int d) {
     asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(cluster_addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ void st_cluster_s32(uint32_t cluster_addr, int v) {
+    asm volatile("st.shared::cluster.s32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
 }
 // The same wait run by all 32 lanes of a converged warp, with a warp-uniform result.
 __device__ __forceinline__ bool wait_or_abort_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
@@ -522,6 +527,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     tc_fence_before();
     __syncthreads();
     if (SPLIT) {
+        // A CTA that gave up on a wait sent nothing (or not everything): tell every CTA of the cluster, so that none
+        // adds a slice that never arrived.  The flag travels with the same barrier as the partial accumulators.
+        if (threadIdx.x == 0 && *s_abort)
+            for (int r = 0; r < csize; ++r) st_cluster_s32(map_to_cta(&s_abort_storage, static_cast<uint32_t>(r)), 1);
         cluster_sync_all();   // the partial accumulators of this CTA's columns have arrived from every K slice
         const int cols_own = BN / csize;
         const int nt = tile_first;                       // one M tile: the tile index is the column tile
@@ -551,15 +560,14 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
 
 static EncodeTiledFn get_encode_tiled() {
     static EncodeTiledFn fn = nullptr;
-    static bool tried = false;
-    if (!tried) {
-        tried = true;
+    static std::once_flag once;
+    std::call_once(once, [] {
         void* ptr = nullptr;
         cudaDriverEntryPointQueryResult qres;
         if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
             qres == cudaDriverEntryPointSuccess)
             fn = reinterpret_cast<EncodeTiledFn>(ptr);
-    }
+    });
     return fn;
 }
 
@@ -609,7 +617,8 @@ static int launch_gemm(EncodeTiledFn encode, const CUtensorMap& map, GemmParams 
     const int64_t tiles = ceil_div<int64_t>(p.M, GM_BM) * ceil_div<int64_t>(p.N, BN);
     const unsigned grid = SPLIT ? static_cast<unsigned>(tiles * split) : static_cast<unsigned>(std::min<int64_t>(tiles, sm_count()));
     auto kern = gemm_tcgen05_kernel<BN, SPLIT>;
-    BT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    static std::atomic<size_t> granted[BT_MAX_DEVICES];
+    if (const int rc = ensure_dynamic_smem(kern, smem, granted)) return rc;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(GM_THREADS);
@@ -679,7 +688,7 @@ extern "C" int bt_gemm_tiled_i8(const int8_t* Xq, const float* sx, const int32_t
     // CTA pairs (cta_group::2, 256 x 256 tiles) once there are enough 256-row tiles to fill the GPU
     const int sms = sm_count();
     bool pair = M > GM_BM && ceil_div<int64_t>(M, 256) * ceil_div<int64_t>(N, 256) >= (sms / 2) * 55 / 100;
-    if (const char* e = std::getenv("BITTORCH_B200_GEMM_PAIR")) pair = std::atoi(e) != 0;      // testing / tuning override
+    if (const int v = tuning(BT_TUNE_GEMM_PAIR); v >= 0) pair = v != 0;      // testing / tuning override
     // rows of the activation tile that are copied: all 128, or M rounded up to the 8-row swizzle atom when M is small
     const int a_rows = (pair || M > GM_BM - 8) ? GM_BM : static_cast<int>(ceil_div<int64_t>(M, 8) * 8);
     CUtensorMap map;
@@ -709,8 +718,8 @@ extern "C" int bt_gemm_tiled_i8(const int8_t* Xq, const float* sx, const int32_t
     int bn = 64;
     if (m_tiles * ceil_div<int64_t>(N, 256) >= sms) bn = 256;
     else if (m_tiles * ceil_div<int64_t>(N, 128) >= sms) bn = 128;
-    if (const char* e = std::getenv("BITTORCH_B200_GEMM_BN")) {      // testing / tuning override
-        const int v = std::atoi(e);
+    {      // testing / tuning override
+        const int v = tuning(BT_TUNE_GEMM_BN);
         if (v == 64 || v == 128 || v == 256) bn = v;
     }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -721,8 +730,8 @@ extern "C" int bt_gemm_tiled_i8(const int8_t* Xq, const float* sx, const int32_t
         const int k_blocks = static_cast<int>(ceil_div<int64_t>(K, GM_BK));
         int split = 8;      // the widest split whose clusters are all resident at once
         while (split > 1 && (tiles > gemm_split_max_clusters(split) || split > k_blocks)) split >>= 1;
-        if (const char* e = std::getenv("BITTORCH_B200_GEMM_SPLIT")) {   // testing / tuning override: 1 disables
-            const int v = std::atoi(e);
+        {   // testing / tuning override: 1 disables
+            const int v = tuning(BT_TUNE_GEMM_SPLIT);
             if ((v == 1 || v == 2 || v == 4 || v == 8) && v <= std::max(1, k_blocks)) split = v;
         }
         if (split > 1) return launch_gemm<256, true>(encode, map, p, st, split);

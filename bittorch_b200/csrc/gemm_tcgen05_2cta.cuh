@@ -270,7 +270,8 @@ static int launch_gemm_pair(EncodeTiledFn encode, const CUtensorMap& map, const 
     const int64_t tiles = ceil_div<int64_t>(p.M, 256) * ceil_div<int64_t>(p.N, G2_BN);
     const unsigned pairs = static_cast<unsigned>(std::min<int64_t>(tiles, sm_count() / 2));
     auto kern = gemm_tcgen05_pair_kernel;
-    BT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(G2_SMEM_BYTES)));
+    static std::atomic<size_t> granted[BT_MAX_DEVICES];
+    if (const int rc = ensure_dynamic_smem(kern, G2_SMEM_BYTES, granted)) return rc;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * pairs);
     cfg.blockDim = dim3(GM_THREADS);

@@ -17,15 +17,15 @@ constexpr int GV_X_PAD = 16;                               // row padding of the
 struct GemvParams {
     const int8_t* Xq;
     const float* sx;
-    const uint8_t* W;      // tiled or public packed weights
+    const uint8_t* W;      // public packed weights [ceil(K/4), N]
     const float* scale;
     const float* bias;
     void* Y;
     int32_t* acc_out;
     int64_t ldy;
     int M, K, N;
-    int KT;                // k tiles (tiled) or packed rows (public) in total
-    int slice_max;         // max tiles / rows per CTA
+    int KT;                // packed rows in total
+    int slice_max;         // max packed rows per CTA
     int y_dtype;
     int x_vec;             // activation rows can be copied 16 bytes at a time
 };
@@ -87,7 +87,6 @@ __device__ __forceinline__ void cluster_reduce_store(const GemvParams& p, const 
         const float y = dequant(acc, p.sx[m], p.scale[n], p.bias ? p.bias[n] : 0.0f, p.bias != nullptr);
         store_out_dt(p.Y, p.y_dtype, static_cast<int64_t>(m) * p.ldy + n, y);
     }
-    BT_STAMP(10);
 }
 
 // ------------------------------------------------------------------------------------
@@ -175,9 +174,9 @@ gemv_packed_kernel(const GemvParams p) {
 // ---- host side -------------------------------------------------------------------------
 
 static int pick_split(int col_blocks, int k_units, int min_units_per_cta) {
-    // Testing / tuning override: BITTORCH_B200_GEMV_SPLIT = 1, 2, 4 or 8.
-    if (const char* e = std::getenv("BITTORCH_B200_GEMV_SPLIT")) {
-        const int v = std::atoi(e);
+    // Testing / tuning override (BT_TUNE_GEMV_SPLIT): 1, 2, 4 or 8.
+    {
+        const int v = tuning(BT_TUNE_GEMV_SPLIT);
         if (v == 1 || v == 2 || v == 4 || v == 8) return (k_units >= v) ? v : 1;
     }
     int S = 1;
@@ -190,8 +189,8 @@ template <typename Kern>
 static int launch_cluster(Kern kern, const char* name, dim3 grid, dim3 block, size_t smem, int S, cudaStream_t st,
                           const GemvParams& p) {
     BT_UNSUPPORTED_IF(smem > 227 * 1024, "%s: needs %zu bytes of shared memory (K too large for this M)", name, smem);
-    if (smem > 48 * 1024)
-        BT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    static std::atomic<size_t> granted[BT_MAX_DEVICES];      // one array per kernel instantiation (Kern)
+    if (const int rc = ensure_dynamic_smem(kern, smem, granted)) return rc;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;

@@ -57,6 +57,7 @@ struct GemvTiledParams {
     int stages;            // ring depth
     int x_dtype, y_dtype;
     int x_vec;             // activation rows can be read with vector loads
+    int serialized;        // host only: launch without programmatic dependent launch (weights were just written)
 };
 
 // Loads 4 consecutive activations of runtime dtype as float.
@@ -96,8 +97,6 @@ gemv_tiled_kernel(const GemvTiledParams p) {
     const int nt = nbl * p.KT;
     const int n_iters = (nt + GT_STAGE_TILES - 1) / GT_STAGE_TILES;
     const uint8_t* src = p.W + static_cast<int64_t>(nb0) * p.KT * TILE_BYTES;
-    BT_STAMP(0);
-    BT_STAMP_CTA(0);
 
     if (tid == 0) {
         for (int s = 0; s < stages; ++s) {
@@ -116,7 +115,6 @@ gemv_tiled_kernel(const GemvTiledParams p) {
     }
     __syncthreads();
     pdl_launch_dependents();
-    BT_STAMP(1);
 
     if (warp == GT_CONSUMER_WARPS) {
         // ---- producer: one lane streams this CTA's contiguous byte range --------------------
@@ -140,8 +138,6 @@ gemv_tiled_kernel(const GemvTiledParams p) {
     } else {
         // ---- consumers --------------------------------------------------------------------------
         pdl_wait();   // activations come from the preceding kernel
-        BT_STAMP(3);
-        BT_STAMP_CTA(1);
         if (FUSED) {
             // thread -> (row, 4-element vector): the 512 consumer threads are split evenly over
             // the next power of two >= M rows; thread j of a row takes vectors j, j+tpr, ...
@@ -168,12 +164,9 @@ gemv_tiled_kernel(const GemvTiledParams p) {
                         mx = fmaxf(fmaxf(fmaxf(mx, fabsf(x[u][0])), fmaxf(fabsf(x[u][1]), fabsf(x[u][2]))), fabsf(x[u][3]));
                 }
             }
-            BT_STAMP(2);
-            BT_STAMP_WARP(32);
             mx = warp_max(mx);                              // a warp never straddles two rows (tpr >= 64)
             if (lane == 0 && row_ok) s_wmax[warp * MR + m] = mx;
             asm volatile("bar.sync 1, %0;" ::"r"(GT_NCONS) : "memory");
-            BT_STAMP(4);
             float amax = 0.0f;
 #pragma unroll
             for (int w = 0; w < GT_CONSUMER_WARPS; ++w) amax = fmaxf(amax, s_wmax[w * MR + (row_ok ? m : 0)]);
@@ -193,7 +186,6 @@ gemv_tiled_kernel(const GemvTiledParams p) {
                         *reinterpret_cast<uint4*>(s_x + mm * xstride + vv * 16) = make_uint4(0, 0, 0, 0);
             }
             if (p.K % 16 != 0) asm volatile("bar.sync 1, %0;" ::"r"(GT_NCONS) : "memory");   // tail bytes are rewritten below
-            BT_STAMP(5);
             int qsum = 0;
             if (row_ok) {
                 const bool emit = (p.xq_out != nullptr) && blockIdx.x == 0;
@@ -227,7 +219,6 @@ gemv_tiled_kernel(const GemvTiledParams p) {
                     }
                 }
             }
-            BT_STAMP(14);
             qsum = warp_sum(qsum);
             if (lane == 0 && row_ok) s_wsum[warp * MR + m] = qsum;
         } else {
@@ -265,8 +256,6 @@ gemv_tiled_kernel(const GemvTiledParams p) {
             for (int w = 0; w < GT_CONSUMER_WARPS; ++w) sum += s_wsum[w * MR + tid];
             s_rowsum[tid] = sum;                             // read after the final CTA barrier
         }
-        BT_STAMP(6);
-        BT_STAMP_CTA(2);
 
         // Lane (g,t), per tile: plane i / word q = four consecutive k of column g + 8(q&1),
         // k = 32t + 8i + 4(q>>1).  acc[m][i][h]: plane i of column g + 8h.
@@ -307,7 +296,6 @@ gemv_tiled_kernel(const GemvTiledParams p) {
                 atomicExch(&s_abort, 1);
                 break;
             }
-            if (it == 0) BT_STAMP(10);
             const uint8_t* tp = lane_ring + s * GT_STAGE_BYTES;
             // one tile: mask the planes, dp4a against the lane's 32 activations of every row
             auto tile = [&](const uint4 wv, const int8_t* xk) {
@@ -368,13 +356,9 @@ gemv_tiled_kernel(const GemvTiledParams p) {
             kt += GT_STAGE_TILES - GT_TPW;                   // on to this warp's tiles of the next stage
             while (kt >= p.KT) { kt -= p.KT; ++nb_local; }
         }
-        BT_STAMP(7);
         if (cur_nb >= 0) flush(cur_nb);
-        BT_STAMP(12);
     }
     __syncthreads();
-    BT_STAMP(9);
-    BT_STAMP_CTA(3);
     if (s_abort) {
         if (tid == 0) {
             // Give copies that may still be in flight a bounded chance to land before the
@@ -399,7 +383,6 @@ gemv_tiled_kernel(const GemvTiledParams p) {
             const float y = dequant(acc, s_sx[m], s_scale[c], s_bias[c], p.bias != nullptr);
             store_out_dt(p.Y, p.y_dtype, static_cast<int64_t>(m) * p.ldy + n, y);
         }
-    BT_STAMP(13);
 }
 
 // ---- host side ------------------------------------------------------------------------------
@@ -422,18 +405,21 @@ static int gemv_tiled_rows_per_launch(int64_t K) {
 template <int MR, bool FUSED>
 static int launch_gemv_tiled_kernel(const GemvTiledParams& p, int grid, size_t smem, cudaStream_t st) {
     auto kern = gemv_tiled_kernel<MR, FUSED>;
-    if (smem > 48 * 1024)
-        BT_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    static std::atomic<size_t> granted[BT_MAX_DEVICES];
+    if (const int rc = ensure_dynamic_smem(kern, smem, granted)) return rc;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(GT_THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
+    // Programmatic dependent launch lets the kernel start (and stream its weights, read scale / bias) while its
+    // predecessor drains; that is only right when the predecessor did not write them.  `serialized` launches
+    // without the attribute: griddepcontrol.* are then no-ops and the kernel is ordinarily stream-ordered.
     cudaLaunchAttribute attrs[1];
     attrs[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attrs[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attrs;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = p.serialized ? 0 : 1;
     BT_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, p));
     return BT_OK;
 }
@@ -496,8 +482,9 @@ static int check_gemv_tiled_args(const char* who, int64_t M, int64_t K, const ui
 }
 
 static GemvTiledParams base_tiled_params(int64_t M, int64_t K, const uint8_t* tiled, int64_t N, const float* scale,
-                                         const float* bias, void* Y, int y_dtype, int64_t ldy, int32_t* acc_out) {
+                                         const float* bias, void* Y, int y_dtype, int64_t ldy, int32_t* acc_out, int flags) {
     GemvTiledParams p = {};
+    p.serialized = (flags & BT_LAUNCH_WEIGHTS_JUST_WRITTEN) != 0;
     p.W = tiled; p.scale = scale; p.bias = bias; p.Y = Y; p.acc_out = acc_out; p.ldy = ldy;
     p.M = static_cast<int>(M); p.K = static_cast<int>(K); p.N = static_cast<int>(N);
     p.y_dtype = y_dtype; p.x_dtype = BT_F32;
@@ -508,12 +495,13 @@ static GemvTiledParams base_tiled_params(int64_t M, int64_t K, const uint8_t* ti
 
 extern "C" int bt_gemv_tiled_i8(const int8_t* Xq, const float* sx, int64_t M, int64_t K, const uint8_t* tiled,
                                 int64_t N, const float* scale, const float* bias, void* Y, int y_dtype, int64_t ldy,
-                                int32_t* acc_out, void* stream) {
+                                int32_t* acc_out, int flags, void* stream) {
     using namespace bt;
     BT_REQUIRE(Xq != nullptr && sx != nullptr, "bt_gemv_tiled_i8: NULL pointer");
+    BT_REQUIRE((flags & ~BT_LAUNCH_WEIGHTS_JUST_WRITTEN) == 0, "bt_gemv_tiled_i8: unknown flags %d", flags);
     int rc = check_gemv_tiled_args("bt_gemv_tiled_i8", M, K, tiled, N, scale, Y, y_dtype, ldy);
     if (rc != BT_OK) return rc;
-    GemvTiledParams p = base_tiled_params(M, K, tiled, N, scale, bias, Y, y_dtype, ldy, acc_out);
+    GemvTiledParams p = base_tiled_params(M, K, tiled, N, scale, bias, Y, y_dtype, ldy, acc_out, flags);
     p.Xq = Xq; p.sx = sx;
     p.x_vec = (K % 16 == 0) && aligned(Xq, 16);
     return launch_gemv_tiled(p, static_cast<cudaStream_t>(stream));
@@ -521,14 +509,15 @@ extern "C" int bt_gemv_tiled_i8(const int8_t* Xq, const float* sx, int64_t M, in
 
 extern "C" int bt_gemv_tiled(const void* X, int x_dtype, int64_t M, int64_t K, int64_t ldx, const uint8_t* tiled,
                              int64_t N, const float* scale, const float* bias, void* Y, int y_dtype, int64_t ldy,
-                             int8_t* xq_out, float* sx_out, int32_t* acc_out, void* stream) {
+                             int8_t* xq_out, float* sx_out, int32_t* acc_out, int flags, void* stream) {
     using namespace bt;
     BT_REQUIRE(X != nullptr, "bt_gemv_tiled: NULL pointer");
+    BT_REQUIRE((flags & ~BT_LAUNCH_WEIGHTS_JUST_WRITTEN) == 0, "bt_gemv_tiled: unknown flags %d", flags);
     BT_REQUIRE(valid_dtype(x_dtype), "bt_gemv_tiled: unknown activation dtype %d", x_dtype);
     BT_REQUIRE(ldx >= K, "bt_gemv_tiled: row stride %lld < K %lld", (long long)ldx, (long long)K);
     int rc = check_gemv_tiled_args("bt_gemv_tiled", M, K, tiled, N, scale, Y, y_dtype, ldy);
     if (rc != BT_OK) return rc;
-    GemvTiledParams p = base_tiled_params(M, K, tiled, N, scale, bias, Y, y_dtype, ldy, acc_out);
+    GemvTiledParams p = base_tiled_params(M, K, tiled, N, scale, bias, Y, y_dtype, ldy, acc_out, flags);
     p.X = X; p.x_dtype = x_dtype; p.ldx = ldx; p.xq_out = xq_out; p.sx_out = sx_out;
     p.x_vec = (K % 4 == 0) && (ldx % 4 == 0) && aligned(X, 4 * dtype_size(x_dtype));
     return launch_gemv_tiled(p, static_cast<cudaStream_t>(stream));

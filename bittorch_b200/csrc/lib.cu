@@ -2,6 +2,7 @@
 // Every kernel file is a header included here, so device globals have one definition
 // and no relocatable device code is needed.
 #include <algorithm>
+#include <atomic>
 #include <cstdlib>
 #include <mutex>
 
@@ -19,15 +20,46 @@ void set_error(const char* fmt, ...) {
 }
 
 int sm_count() {
-    static int cached[64] = {0};
+    static std::atomic<int> cached[BT_MAX_DEVICES];            // zero-initialised; a race only repeats the query
     int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
-    if (cached[dev] == 0) {
-        int n = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= BT_MAX_DEVICES) return 148;
+    int n = cached[dev].load(std::memory_order_relaxed);
+    if (n == 0) {
         if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-        cached[dev] = n;
+        cached[dev].store(n, std::memory_order_relaxed);
     }
-    return cached[dev];
+    return n;
+}
+
+// ---- kernel-selection overrides (tests, tuning) ------------------------------------------------
+static std::atomic<int> g_tuning[BT_TUNE_COUNT];
+static std::once_flag g_tuning_once;
+
+static void tuning_init() {
+    static const char* const env_names[BT_TUNE_COUNT] = {"BITTORCH_B200_GEMM_PAIR", "BITTORCH_B200_GEMM_BN",
+                                                         "BITTORCH_B200_GEMM_SPLIT", "BITTORCH_B200_GEMV_SPLIT"};
+    for (int k = 0; k < BT_TUNE_COUNT; ++k) {
+        const char* e = std::getenv(env_names[k]);
+        g_tuning[k].store(e != nullptr ? std::atoi(e) : -1, std::memory_order_relaxed);
+    }
+}
+
+int tuning(int knob) {
+    std::call_once(g_tuning_once, tuning_init);
+    return (knob >= 0 && knob < BT_TUNE_COUNT) ? g_tuning[knob].load(std::memory_order_relaxed) : -1;
+}
+
+// A wait that nothing will ever satisfy, with a small poll limit: exercises the give-up path of the bounded
+// waits (status word, normal return) without any kernel of the library having to fail.
+__global__ void wait_timeout_selftest_kernel(int polls) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        mbar_fence_init();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && !mbar_wait_bounded(&bar, 0, static_cast<uint32_t>(polls))) report_wait_timeout();
+    __syncthreads();
 }
 
 }  // namespace bt
@@ -68,19 +100,17 @@ extern "C" int bt_dummy(const void* src, void* dst, size_t bytes, void* stream) 
     return BT_OK;
 }
 
-#ifdef BT_TRACE
-// Bring-up aid (only in -DBT_TRACE builds): copies the kernel timeline stamps to the host.
-extern "C" int bt_trace_read(unsigned long long* out64) {
+extern "C" int bt_set_tuning(int knob, int value) {
     using namespace bt;
-    BT_CUDA_OK(cudaDeviceSynchronize());
-    BT_CUDA_OK(cudaMemcpyFromSymbol(out64, g_trace, sizeof(unsigned long long) * 128));
+    BT_REQUIRE(knob >= 0 && knob < BT_TUNE_COUNT, "bt_set_tuning: unknown knob %d", knob);
+    tuning(knob);                                              // the environment is read before the first override
+    g_tuning[knob].store(value, std::memory_order_relaxed);
     return BT_OK;
 }
-extern "C" int bt_trace_read_cta(unsigned long long* out64, unsigned int* sm) {
+
+extern "C" int bt_selftest_wait_timeout(void* stream) {
     using namespace bt;
-    BT_CUDA_OK(cudaDeviceSynchronize());
-    BT_CUDA_OK(cudaMemcpyFromSymbol(out64, g_trace_cta, sizeof(unsigned long long) * 4096 * 4));
-    BT_CUDA_OK(cudaMemcpyFromSymbol(sm, g_trace_sm, sizeof(unsigned int) * 4096));
+    wait_timeout_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(2048);
+    BT_LAUNCH_OK("wait_timeout_selftest_kernel");
     return BT_OK;
 }
-#endif

@@ -94,7 +94,7 @@ template <bool PACKED>
 static int launch_linear_float(const char* who, const void* X, int x_dtype, int64_t M, int64_t K, const void* W, int64_t N,
                                const float* scale, const float* bias, void* Y, void* stream) {
     BT_REQUIRE(X && W && scale && Y, "%s: NULL pointer", who);
-    BT_REQUIRE(valid_dtype(x_dtype), "%s: unknown dtype %d", who, x_dtype);
+    BT_REQUIRE(valid_dtype(x_dtype) || x_dtype == BT_F64, "%s: unknown dtype %d", who, x_dtype);
     BT_REQUIRE(M > 0 && K > 0, "%s: X is empty", who);
     BT_REQUIRE(N > 0, "%s: weight is empty", who);
     BT_UNSUPPORTED_IF(M > (int64_t{1} << 30) || N > (int64_t{1} << 30) || K > (int64_t{1} << 30), "%s: shape too large", who);
@@ -104,6 +104,8 @@ static int launch_linear_float(const char* who, const void* X, int x_dtype, int6
     const int m = static_cast<int>(M), k = static_cast<int>(K), n = static_cast<int>(N);
     if (x_dtype == BT_F32)
         linear_float_kernel<float, PACKED><<<grid, LF_THREADS, 0, st>>>(static_cast<const float*>(X), m, k, W, n, scale, bias, static_cast<float*>(Y));
+    else if (x_dtype == BT_F64)   // float64 containers, float32 arithmetic (csrc/kernels/ternary_gemm.cu:56-61)
+        linear_float_kernel<double, PACKED><<<grid, LF_THREADS, 0, st>>>(static_cast<const double*>(X), m, k, W, n, scale, bias, static_cast<double*>(Y));
     else if (x_dtype == BT_F16)
         linear_float_kernel<__half, PACKED><<<grid, LF_THREADS, 0, st>>>(static_cast<const __half*>(X), m, k, W, n, scale, bias, static_cast<__half*>(Y));
     else

@@ -181,6 +181,34 @@ __global__ void unpack_codes_kernel(const uint8_t* __restrict__ packed_T, int64_
     }
 }
 
+// Row layout uint8 [N, ceil(K/4)] (bittorch/quant/ternary_packed.py:22-75): one thread per packed byte, codes read
+// and bytes written along k, so both sides coalesce without a transpose.
+__global__ void pack_codes_rows_kernel(const int8_t* __restrict__ codes, int64_t N, int64_t K, uint8_t* __restrict__ packed) {
+    const int64_t KB = (K + 3) / 4, total = N * KB;
+    for (int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; idx < total;
+         idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t n = idx / KB, kb = idx % KB;
+        uint32_t byte = 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int64_t k = kb * 4 + i;
+            if (k < K) byte |= two_bit(codes[n * K + k]) << (2 * i);
+        }
+        packed[idx] = static_cast<uint8_t>(byte);
+    }
+}
+
+// Inverse of the row layout; reserved pattern 11 -> 0 (bittorch/quant/ternary_packed.py:112-115).
+__global__ void unpack_codes_rows_kernel(const uint8_t* __restrict__ packed, int64_t N, int64_t K, int8_t* __restrict__ codes) {
+    const int64_t KB = (K + 3) / 4, total = N * K;
+    for (int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; idx < total;
+         idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t n = idx / K, k = idx % K;
+        const uint32_t c = (packed[n * KB + (k >> 2)] >> (2 * (k & 3))) & 3u;
+        codes[idx] = static_cast<int8_t>((c == 1u) - (c == 2u));
+    }
+}
+
 template <typename T>
 static int launch_quantize_pack(const void* W, int64_t N, int64_t K, int64_t ldw, float tf, uint8_t* packed_T,
                                 float* scale, int8_t* codes, void* tern, cudaStream_t st) {
@@ -227,5 +255,27 @@ extern "C" int bt_unpack_codes(const uint8_t* packed_T, int64_t N, int64_t K, in
     const unsigned grid = static_cast<unsigned>(std::min<int64_t>(ceil_div<int64_t>(total, 256), sm_count() * 16));
     unpack_codes_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(packed_T, N, K, codes);
     BT_LAUNCH_OK("unpack_codes_kernel");
+    return BT_OK;
+}
+
+extern "C" int bt_pack_codes_rows(const int8_t* codes, int64_t N, int64_t K, uint8_t* packed, void* stream) {
+    using namespace bt;
+    BT_REQUIRE(codes != nullptr && packed != nullptr, "bt_pack_codes_rows: NULL pointer");
+    BT_REQUIRE(N > 0 && K > 0, "bt_pack_codes_rows: empty weight");
+    const int64_t total = N * ceil_div<int64_t>(K, 4);
+    const unsigned grid = static_cast<unsigned>(std::min<int64_t>(ceil_div<int64_t>(total, 256), sm_count() * 16));
+    pack_codes_rows_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(codes, N, K, packed);
+    BT_LAUNCH_OK("pack_codes_rows_kernel");
+    return BT_OK;
+}
+
+extern "C" int bt_unpack_codes_rows(const uint8_t* packed, int64_t N, int64_t K, int8_t* codes, void* stream) {
+    using namespace bt;
+    BT_REQUIRE(codes != nullptr && packed != nullptr, "bt_unpack_codes_rows: NULL pointer");
+    BT_REQUIRE(N > 0 && K > 0, "bt_unpack_codes_rows: empty weight");
+    const int64_t total = N * K;
+    const unsigned grid = static_cast<unsigned>(std::min<int64_t>(ceil_div<int64_t>(total, 256), sm_count() * 16));
+    unpack_codes_rows_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(packed, N, K, codes);
+    BT_LAUNCH_OK("unpack_codes_rows_kernel");
     return BT_OK;
 }

@@ -118,6 +118,16 @@ class TernaryLinear(nn.Module):
         bias = self.bias.to(x.dtype) if self.bias is not None else None
         return F.linear(x, w_effective, bias)
 
+    def invalidate_cache(self) -> None:
+        """Forget the packed copy of the weight that inference-mode forwards reuse: the next forward re-quantizes.
+        Needed only after an in-place write through ``weight.data`` that changes so few elements that the sampled
+        content check can miss it (``nn/ternary_linear_cuda.py``: ``content_fingerprint``)."""
+        self._cache.invalidate()
+
+    def _load_from_state_dict(self, *args, **kwargs):
+        self._cache.invalidate()
+        return super()._load_from_state_dict(*args, **kwargs)
+
     def extra_repr(self) -> str:
         return (f"in_features={self.in_features}, out_features={self.out_features}, bias={self.bias is not None}, "
                 f"threshold_factor={self.threshold_factor}, per_channel={self.per_channel}, "

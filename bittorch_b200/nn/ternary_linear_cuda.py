@@ -19,29 +19,64 @@ from torch import Tensor
 from .._ext import require_ext
 
 
+def content_fingerprint(*tensors: Tensor) -> tuple:
+    """A few numbers computed from about a thousand evenly spaced elements of each tensor, read back to the host
+    (one small device-to-host copy, which synchronises the stream).
+
+    The caches of this package key on a tensor's address and in-place version counter; a write through ``.data``
+    (``p.data.copy_(w)``, the usual way of loading weights by hand) changes neither, so the key is completed with
+    this content check.  It sees every bulk update (copies, scalings, optimizer steps); a write that touches only a
+    few elements can fall between the samples - after such a write call ``invalidate_cache()`` on the module.
+    """
+    parts = []
+    for t in tensors:
+        flat = t.detach().reshape(-1)
+        step = max(1, flat.numel() // 1024)
+        sample = flat[::step][:1024].to(torch.float64)
+        weights = torch.arange(1, sample.numel() + 1, dtype=torch.float64, device=sample.device)
+        parts += [sample.sum(), (sample * weights).sum()]      # the second sum also sees permutations
+    return tuple(torch.stack(parts).tolist())
+
+
+def capturing() -> bool:
+    """True while the current CUDA stream is being captured into a graph (no host read-back possible)."""
+    return torch.cuda.is_available() and torch.cuda.is_current_stream_capturing()
+
+
 class PackedWeightCache:
     """Packed/tiled copies of a master weight, valid while the parameter is unchanged.
 
-    Keyed on the parameter's storage address, in-place version counter, dtype and
-    threshold: an optimizer step bumps the version and the next forward re-quantizes.
+    Keyed on the parameter's storage address, in-place version counter, dtype and threshold (an optimizer step
+    bumps the version and the next forward re-quantizes) plus ``content_fingerprint`` of the weight, which catches
+    writes through ``.data`` that the version counter misses.  The fingerprint costs a host synchronisation per
+    forward; it is skipped during CUDA-graph capture (captured weights must not change anyway) and can be switched
+    off with ``verify = False`` once a model's weights are final.
     """
+
+    verify = True
 
     def __init__(self) -> None:
         self.key = None
+        self.fingerprint = None
         self.packed_T: Optional[Tensor] = None
         self.tiled: Optional[Tensor] = None
         self.scale: Optional[Tensor] = None   # float32 [N]
 
+    def invalidate(self) -> None:
+        self.key = None
+
     def lookup(self, weight: Tensor, threshold_factor: float):
+        """Returns (key, fingerprint, hit)."""
         key = (weight.data_ptr(), weight._version, weight.dtype, tuple(weight.shape), float(threshold_factor))
-        return key, (self.key == key)
+        check = self.verify and not capturing()
+        fp = content_fingerprint(weight) if check else None
+        hit = self.key == key and (not check or fp == self.fingerprint)
+        return key, fp, hit
 
 
 def usable_cache(cache: Optional[PackedWeightCache]) -> Optional[PackedWeightCache]:
-    """The cache is consulted only for inference-style calls (grad mode off, no autocast):
-    training forwards re-quantize every time, like the reference, so an update made
-    through ``weight.data`` (which does not bump the version counter) is never missed
-    while training, and autocast's temporary fp16 copies are never mistaken for the
+    """The cache is consulted only for inference-style calls (grad mode off, no autocast): training forwards
+    re-quantize every time, like the reference, and autocast's temporary fp16 copies are never mistaken for the
     parameter."""
     if cache is None or torch.is_grad_enabled() or torch.is_autocast_enabled("cuda"):
         return None
@@ -49,17 +84,30 @@ def usable_cache(cache: Optional[PackedWeightCache]) -> Optional[PackedWeightCac
 
 
 def _quantized(weight: Tensor, threshold_factor: float, cache: Optional[PackedWeightCache]):
+    """(packed_T, tiled, scale float32, fresh): ``fresh`` says that the buffers were written by kernels enqueued just
+    now, so the first kernel that reads them must be launched stream-ordered."""
     C = require_ext()
+    key = fp = None
     if cache is not None:
-        key, hit = cache.lookup(weight, threshold_factor)
+        key, fp, hit = cache.lookup(weight, threshold_factor)
         if hit:
-            return cache.packed_T, cache.tiled, cache.scale
-    out = C.quantize_pack(weight, threshold_factor, want_packed=True)
-    packed_T, scale = out["packed_T"], out["scale"]
+            return cache.packed_T, cache.tiled, cache.scale, False
+    if weight.dtype == torch.float64:
+        # float64 masters (gradient checks): the reference's own expression in float64
+        # (bittorch/quant/ternary.py:122-142), then the packer kernel
+        mag = weight.abs()
+        scale64 = mag.max(dim=1, keepdim=True).values.clamp(min=1e-8)
+        tern = torch.where(mag > threshold_factor * scale64, torch.sign(weight), torch.zeros_like(weight))
+        packed_T, scale = C.pack_codes(tern.to(torch.int8)), scale64.squeeze(1).to(torch.float32)
+    else:
+        out = C.quantize_pack(weight, threshold_factor, want_packed=True)
+        packed_T, scale = out["packed_T"], out["scale"]
     tiled = C.retile(packed_T, weight.shape[1])
     if cache is not None:
-        cache.key, cache.packed_T, cache.tiled, cache.scale = key, packed_T, tiled, scale
-    return packed_T, tiled, scale
+        if fp is None and cache.verify and not capturing():
+            fp = content_fingerprint(weight)
+        cache.key, cache.fingerprint, cache.packed_T, cache.tiled, cache.scale = key, fp, packed_T, tiled, scale
+    return packed_T, tiled, scale, True
 
 
 class TernaryLinearCUDAFunction(torch.autograd.Function):
@@ -82,13 +130,14 @@ class TernaryLinearCUDAFunction(torch.autograd.Function):
         if x.shape[-1] != weight.shape[1]:
             raise RuntimeError("input K doesn't match weight K")
         n, k = weight.shape
-        packed_T, tiled, scale = _quantized(weight.detach(), threshold_factor, cache)
+        packed_T, tiled, scale, fresh = _quantized(weight.detach(), threshold_factor, cache)
         b32 = None if bias is None else bias.detach().to(torch.float32).contiguous()
         x2d = x.detach().contiguous().reshape(-1, k)
-        if C.activation_mode() == "float":
+        if C.activation_mode() == "float" or x2d.dtype == torch.float64:      # float64 has no int8 path
             y2d = C.ternary_linear_packed_forward(x2d, packed_T, scale, b32, k)
         else:
-            y2d = C.int8_linear_tiled(x2d, tiled, k, n, scale, b32)
+            fresh = fresh or (b32 is not None and b32.data_ptr() != bias.data_ptr())     # a float32 copy made just now
+            y2d = C.int8_linear_tiled(x2d, tiled, k, n, scale, b32, fresh_weights=fresh)
         ctx.save_for_backward(x, packed_T, scale)
         ctx.has_bias = bias is not None
         ctx.in_features = k
@@ -146,6 +195,15 @@ class TernaryLinearCUDA(nn.Module):
             raise RuntimeError("TernaryLinearCUDA requires CUDA tensors. Use TernaryLinear for CPU.")
         return TernaryLinearCUDAFunction.apply(x, self.weight, self.bias, self.threshold_factor, self.per_channel,
                                                usable_cache(self._cache))
+
+    def invalidate_cache(self) -> None:
+        """Forget the packed copy of the weight: the next forward re-quantizes.  Needed only after an in-place
+        write through ``weight.data`` that changes so few elements that the sampled content check can miss it."""
+        self._cache.invalidate()
+
+    def _load_from_state_dict(self, *args, **kwargs):
+        self._cache.invalidate()
+        return super()._load_from_state_dict(*args, **kwargs)
 
     def get_quantized_weight(self):
         from ..quant.ternary import ternary_quantize

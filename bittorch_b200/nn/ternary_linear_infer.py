@@ -37,18 +37,39 @@ class TernaryLinearInference(nn.Module):
         self._scale32: Optional[Tensor] = None
         self._bias32: Optional[Tensor] = None
 
+    # Check the buffers' contents (a sampled fingerprint, one host synchronisation per forward) next to their
+    # addresses and version counters, so that a write through ``weight_packed.data`` / ``scale.data`` is seen.
+    # Set to False on a module (or on the class) once the weights are final and the eager call rate matters.
+    verify_buffers = True
+
+    def invalidate_cache(self) -> None:
+        """Rebuild the derived buffers (tiled weights, float32 scale / bias) on the next forward."""
+        self._derived_key = None
+
+    def _load_from_state_dict(self, *args, **kwargs):
+        self.invalidate_cache()
+        return super()._load_from_state_dict(*args, **kwargs)
+
     def _derived(self):
-        """Tiled weights and float32 scale/bias, rebuilt when a buffer was replaced or written."""
+        """(tiled weights, float32 scale, float32 bias, fresh): rebuilt when a buffer was replaced or written;
+        ``fresh`` says they were written by kernels enqueued just now."""
+        from .ternary_linear_cuda import capturing, content_fingerprint
+
         wp, sc, b = self.weight_packed, self.scale, self.bias
         key = (wp.data_ptr(), wp._version, sc.data_ptr(), sc._version,
                None if b is None else (b.data_ptr(), b._version))
-        if key != self._derived_key:
+        if self.verify_buffers and not capturing():
+            key += content_fingerprint(wp, sc, *(() if b is None else (b,)))
+        elif self._derived_key is not None:
+            key += self._derived_key[len(key):]                # keep comparing addresses and versions only
+        fresh = key != self._derived_key
+        if fresh:
             C = require_ext()
             self._tiled = C.retile(wp, self.in_features)
             self._scale32 = sc.to(torch.float32).contiguous()
             self._bias32 = None if b is None else b.to(torch.float32).contiguous()
             self._derived_key = key
-        return self._tiled, self._scale32, self._bias32
+        return self._tiled, self._scale32, self._bias32, fresh
 
     def forward(self, x: Tensor) -> Tensor:
         """x: (*, in_features) CUDA tensor -> (*, out_features), dtype of x."""
@@ -58,11 +79,11 @@ class TernaryLinearInference(nn.Module):
             raise RuntimeError("input K doesn't match in_features")
         if x.numel() == 0:
             raise RuntimeError("X is empty")
-        if C.activation_mode() == "float":
+        if C.activation_mode() == "float" or x.dtype == torch.float64:
             return C.ternary_linear_packed_forward(x, self.weight_packed, self.scale, self.bias, self.in_features)
-        tiled, s32, b32 = self._derived()
+        tiled, s32, b32, fresh = self._derived()
         x2d = x.contiguous().reshape(-1, self.in_features)
-        y = C.int8_linear_tiled(x2d, tiled, self.in_features, self.out_features, s32, b32)
+        y = C.int8_linear_tiled(x2d, tiled, self.in_features, self.out_features, s32, b32, fresh_weights=fresh)
         return y.reshape(*x.shape[:-1], self.out_features)
 
     def extra_repr(self) -> str:

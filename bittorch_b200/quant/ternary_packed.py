@@ -2,7 +2,7 @@
 
 Same functions and byte format as the reference's ``bittorch/quant/ternary_packed.py``
 (00 = 0, 01 = +1, 10 = -1; weight j of a group of four in bits 2j+1:2j; K padded to a
-multiple of four), computed by ``bt_pack_codes`` / ``bt_unpack_codes`` /
+multiple of four), computed by ``bt_pack_codes[_rows]`` / ``bt_unpack_codes[_rows]`` /
 ``bt_quantize_pack``.  Tensors must be CUDA tensors.
 """
 
@@ -31,8 +31,8 @@ def pack_ternary_transposed(w_tern: Tensor) -> Tuple[Tensor, int]:
 
 def pack_ternary(w_tern: Tensor) -> Tuple[Tensor, int]:
     """[N,K] ternary -> (uint8 [N, ceil(K/4)], K) (bittorch/quant/ternary_packed.py:22-75)."""
-    packed_t, k = pack_ternary_transposed(w_tern)
-    return packed_t.T.contiguous(), k
+    codes = _codes_i8(w_tern)
+    return require_ext().pack_codes_rows(codes), int(w_tern.shape[1])
 
 
 def unpack_ternary_transposed(packed_T: Tensor, in_features: int) -> Tensor:
@@ -47,7 +47,8 @@ def unpack_ternary(packed: Tensor, in_features: int) -> Tensor:
     """uint8 [N, ceil(K/4)] -> int8 [N,K] (bittorch/quant/ternary_packed.py:78-120)."""
     if packed.dim() != 2:
         raise ValueError(f"Expected 2D tensor, got {packed.dim()}D")
-    return unpack_ternary_transposed(packed.T.contiguous(), in_features)
+    require_cuda_tensor(packed, "packed")
+    return require_ext().unpack_codes_rows(packed, int(in_features))
 
 
 def pack_ternary_with_scale(w_tern: Tensor, scale: Tensor) -> Tuple[Tensor, Tensor, int]:

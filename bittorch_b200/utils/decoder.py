@@ -120,7 +120,9 @@ def fuse_inference_columns(layers) -> TernaryLinearInference:
     bias = None
     if any(l.bias is not None for l in layers):
         bias = torch.cat([l.bias if l.bias is not None else torch.zeros_like(l.scale) for l in layers])
-    return TernaryLinearInference(k, sum(l.out_features for l in layers), wp, scale, bias)
+    fused = TernaryLinearInference(k, sum(l.out_features for l in layers), wp, scale, bias)
+    fused.verify_buffers = False          # private copies: nobody else can write them
+    return fused
 
 
 class _FusedColumns:
@@ -137,8 +139,15 @@ class _FusedColumns:
         return all(isinstance(l, TernaryLinearInference) for l in self.layers)
 
     def __call__(self, x: Tensor):
+        from ..nn.ternary_linear_cuda import capturing, content_fingerprint
+
         key = tuple((l.weight_packed.data_ptr(), l.weight_packed._version, l.scale.data_ptr(), l.scale._version)
                     for l in self.layers)
+        if all(l.verify_buffers for l in self.layers) and not capturing():
+            # writes through .data leave addresses and versions alone: compare sampled contents too
+            key += content_fingerprint(*[t for l in self.layers for t in (l.weight_packed, l.scale)])
+        elif self._key is not None:
+            key += self._key[len(key):]
         if key != self._key:
             self._fused = fuse_inference_columns(self.layers)
             self._key = key

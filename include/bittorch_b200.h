@@ -42,6 +42,30 @@ extern "C" {
 #define BT_F32 0
 #define BT_F16 1
 #define BT_BF16 2
+/* float64: accepted by the two floating-point-activation entry points only
+ * (bt_linear_unpacked, bt_linear_packed_float), as the reference dispatches them
+ * (AT_DISPATCH_FLOATING_TYPES_AND_HALF, csrc/kernels/ternary_gemm.cu:248,
+ * csrc/kernels/ternary_gemm_production.cu:331). */
+#define BT_F64 3
+
+/* Launch flags of the decode entry points (bt_gemv_tiled, bt_gemv_tiled_i8). */
+#define BT_LAUNCH_DEFAULT 0
+/* The weights, scales or bias of this call were written by work enqueued just before
+ * it on the same stream (a fresh quantize / re-tile / copy): launch fully
+ * stream-ordered.  Without the flag the decode kernel is launched with programmatic
+ * dependent launch and reads scale / bias and starts streaming its WEIGHTS before the
+ * preceding kernel has finished (only the activations are read after the dependency
+ * wait), which is what lets consecutive layers overlap. */
+#define BT_LAUNCH_WEIGHTS_JUST_WRITTEN 1
+
+/* Kernel-selection overrides for tests and tuning, bt_set_tuning(knob, value); value -1
+ * (the default) lets the library choose.  Each knob's initial value comes from the
+ * environment variable named beside it, read once. */
+#define BT_TUNE_GEMM_PAIR 0   /* BITTORCH_B200_GEMM_PAIR : 1 / 0 force the CTA-pair GEMM on / off */
+#define BT_TUNE_GEMM_BN 1     /* BITTORCH_B200_GEMM_BN   : 64 / 128 / 256 output-tile width */
+#define BT_TUNE_GEMM_SPLIT 2  /* BITTORCH_B200_GEMM_SPLIT: 1 / 2 / 4 / 8 K split of the narrow-batch GEMM */
+#define BT_TUNE_GEMV_SPLIT 3  /* BITTORCH_B200_GEMV_SPLIT: 1 / 2 / 4 / 8 K split of bt_gemv_packed_i8 */
+#define BT_TUNE_COUNT 4
 
 /* Largest M handled by the decode (GEMV) kernels. */
 #define BT_GEMV_MAX_M 16
@@ -60,6 +84,18 @@ const char* bt_last_error(void);
  * last call.  Synchronises `stream`.
  */
 int bt_device_status(int* status_host, void* stream);
+
+/* Process-wide; takes effect for later calls.  No counterpart in the reference. */
+int bt_set_tuning(int knob, int value);
+
+/*
+ * Enqueues a one-warp kernel whose bounded wait can never be satisfied and gives up
+ * after a few thousand polls (microseconds): afterwards bt_device_status() reads
+ * BT_ERR_DEVICE_WAIT once and then 0 again.  Lets a caller check the give-up path of
+ * the library's device-side waits - status word, normal kernel exit, usable context -
+ * without any real kernel failing.  No counterpart in the reference.
+ */
+int bt_selftest_wait_timeout(void* stream);
 
 /*
  * Device-to-device clone of `bytes` bytes.
@@ -95,6 +131,15 @@ int bt_quantize_pack(const void* W, int w_dtype, int64_t N, int64_t K, int64_t l
  */
 int bt_pack_codes(const int8_t* codes, int64_t N, int64_t K, uint8_t* packed_T, void* stream);
 int bt_unpack_codes(const uint8_t* packed_T, int64_t N, int64_t K, int8_t* codes, void* stream);
+
+/*
+ * The same bytes in the row layout uint8 [N, ceil(K/4)] (byte [n,kb] = codes of
+ * W[n,4kb..4kb+3]): pack_ternary / unpack_ternary
+ * (bittorch/quant/ternary_packed.py:22-75, 78-120) and the browser runtime's weight
+ * format (js/src/core/types.ts:9).
+ */
+int bt_pack_codes_rows(const int8_t* codes, int64_t N, int64_t K, uint8_t* packed, void* stream);
+int bt_unpack_codes_rows(const uint8_t* packed, int64_t N, int64_t K, int8_t* codes, void* stream);
 
 /*
  * Per-token int8 activation quantizer (one scale per row of X):
@@ -134,13 +179,16 @@ int bt_untile_packed(const uint8_t* tiled, int64_t K, int64_t N, uint8_t* packed
  *
  * Xq int8 [M,K] contiguous; sx float32 [M]; scale float32 [N]; bias float32 [N] or NULL;
  * Y [M,N] row stride ldy, dtype y_dtype; acc_out int32 [M,N] or NULL (parity checks).
+ * bt_gemv_tiled_i8 / bt_gemv_tiled: `flags` is BT_LAUNCH_DEFAULT, or
+ * BT_LAUNCH_WEIGHTS_JUST_WRITTEN when tiled / scale / bias were produced by the work
+ * enqueued just before this call (see the flag's comment): PRECONDITION of the default.
  */
 int bt_gemv_packed_i8(const int8_t* Xq, const float* sx, int64_t M, int64_t K,
                       const uint8_t* packed_T, int64_t N, const float* scale, const float* bias,
                       void* Y, int y_dtype, int64_t ldy, int32_t* acc_out, void* stream);
 int bt_gemv_tiled_i8(const int8_t* Xq, const float* sx, int64_t M, int64_t K,
                      const uint8_t* tiled, int64_t N, const float* scale, const float* bias,
-                     void* Y, int y_dtype, int64_t ldy, int32_t* acc_out, void* stream);
+                     void* Y, int y_dtype, int64_t ldy, int32_t* acc_out, int flags, void* stream);
 
 /*
  * Decode-size packed ternary linear straight from floating-point activations: the
@@ -158,7 +206,7 @@ int bt_gemv_tiled_i8(const int8_t* Xq, const float* sx, int64_t M, int64_t K,
 int bt_gemv_tiled(const void* X, int x_dtype, int64_t M, int64_t K, int64_t ldx,
                   const uint8_t* tiled, int64_t N, const float* scale, const float* bias,
                   void* Y, int y_dtype, int64_t ldy, int8_t* xq_out, float* sx_out,
-                  int32_t* acc_out, void* stream);
+                  int32_t* acc_out, int flags, void* stream);
 
 /*
  * Prefill-size packed ternary linear on int8 activations (any M >= 1), same
@@ -173,6 +221,8 @@ int bt_gemv_tiled(const void* X, int x_dtype, int64_t M, int64_t K, int64_t ldx,
  * tiles) when there are enough such tiles; one CTA per 128 x {256,128,64} tile otherwise; and, up to
  * 32 rows, full-width tiles with K split over a thread-block cluster whose partial accumulators meet
  * in distributed shared memory.  None uses global scratch memory; results do not depend on the choice.
+ * All three wait for the preceding kernel before their first global read, so the call is
+ * stream-ordered with respect to every operand (no precondition on freshly written weights).
  */
 int bt_gemm_tiled_i8(const int8_t* Xq, const float* sx, const int32_t* xsum, int64_t M, int64_t K,
                      const uint8_t* tiled, int64_t N, const float* scale, const float* bias,
@@ -182,7 +232,9 @@ int bt_gemm_tiled_i8(const int8_t* Xq, const float* sx, const int32_t* xsum, int
  * Unpacked-weight linear with floating-point activations, fp32 accumulation:
  *   Y[b,n] = (sum_k X[b,k] * W[n,k]) * scale[n] + bias[n],   W int8 [N,K]
  * Replaces `_C.ternary_linear_forward` (csrc/core/dispatch.cpp:52-87;
- * csrc/kernels/ternary_gemm.cu:41-177).
+ * csrc/kernels/ternary_gemm.cu:41-177).  x_dtype may be BT_F64: X and Y are float64
+ * and the arithmetic is still float32, as in the reference (`static_cast<float>(X[...])`,
+ * csrc/kernels/ternary_gemm.cu:56-61); scale / bias stay float32 on this side of the boundary.
  */
 int bt_linear_unpacked(const void* X, int x_dtype, int64_t M, int64_t K,
                        const int8_t* W, int64_t N, const float* scale, const float* bias,
@@ -194,6 +246,7 @@ int bt_linear_unpacked(const void* X, int x_dtype, int64_t M, int64_t K,
  *   Y[b,n] = (sum_k X[b,k] * T[n,k]) * scale[n] + bias[n]
  * Replaces the float arithmetic of `_C.ternary_linear_packed_forward`
  * (csrc/kernels/ternary_gemm_production.cu:53-250).  Reads the public layout.
+ * x_dtype may be BT_F64.
  */
 int bt_linear_packed_float(const void* X, int x_dtype, int64_t M, int64_t K,
                            const uint8_t* packed_T, int64_t N, const float* scale, const float* bias,

@@ -40,3 +40,23 @@ def oracle():
 
     _oracle.build()
     return _oracle
+
+
+EMULATED = os.environ.get("BITTORCH_B200_EMULATED") == "1"      # GPU-marked tests run against tests/emu on the CPU
+needs_real_gpu = pytest.mark.skipif(EMULATED, reason="checks the CUDA library itself, not host logic")
+
+
+@pytest.fixture
+def tuning():
+    """Kernel-selection overrides (bt_set_tuning) that are undone when the test ends."""
+    from bittorch_b200 import _C
+
+    touched = []
+
+    def set_knob(knob: int, value: int) -> None:
+        touched.append(knob)
+        _C.set_tuning(knob, value)
+
+    yield set_knob
+    for knob in touched:
+        _C.set_tuning(knob, -1)

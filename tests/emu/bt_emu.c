@@ -68,6 +68,7 @@ static uint16_t float_to_half(float v) {
 
 static float load_elem(const void* p, int dtype, int64_t i) {
     if (dtype == BT_F32) return ((const float*)p)[i];
+    if (dtype == BT_F64) return (float)((const double*)p)[i];
     if (dtype == BT_F16) return half_to_float(((const uint16_t*)p)[i]);
     uint32_t u = (uint32_t)((const uint16_t*)p)[i] << 16;
     float r;
@@ -77,6 +78,7 @@ static float load_elem(const void* p, int dtype, int64_t i) {
 
 static void store_elem(void* p, int dtype, int64_t i, float v) {
     if (dtype == BT_F32) ((float*)p)[i] = v;
+    else if (dtype == BT_F64) ((double*)p)[i] = (double)v;
     else if (dtype == BT_F16) ((uint16_t*)p)[i] = float_to_half(v);
     else {
         float r = round_to_bf16(v);
@@ -126,10 +128,26 @@ static int8_t* codes_from_tiled(const uint8_t* tiled, int64_t K, int64_t N) {
 int bt_version(void) { return 100; }
 const char* bt_last_error(void) { return g_error; }
 
+static int g_status = 0;
+static int g_tuning[BT_TUNE_COUNT] = {-1, -1, -1, -1};
+
 int bt_device_status(int* status_host, void* stream) {
     (void)stream;
     REQUIRE(status_host != NULL, "bt_device_status: NULL pointer");
-    *status_host = 0;
+    *status_host = g_status;
+    g_status = 0;
+    return BT_OK;
+}
+
+int bt_set_tuning(int knob, int value) {
+    REQUIRE(knob >= 0 && knob < BT_TUNE_COUNT, "bt_set_tuning: unknown knob %d", knob);
+    g_tuning[knob] = value;                                    /* recorded; the emulation has one code path */
+    return BT_OK;
+}
+
+int bt_selftest_wait_timeout(void* stream) {
+    (void)stream;
+    g_status = BT_ERR_DEVICE_WAIT;
     return BT_OK;
 }
 
@@ -289,8 +307,9 @@ int bt_gemv_packed_i8(const int8_t* Xq, const float* sx, int64_t M, int64_t K, c
 
 int bt_gemv_tiled_i8(const int8_t* Xq, const float* sx, int64_t M, int64_t K, const uint8_t* tiled, int64_t N,
                      const float* scale, const float* bias, void* Y, int y_dtype, int64_t ldy, int32_t* acc_out,
-                     void* stream) {
+                     int flags, void* stream) {
     (void)stream;
+    REQUIRE((flags & ~BT_LAUNCH_WEIGHTS_JUST_WRITTEN) == 0, "bt_gemv_tiled_i8: unknown flags %d", flags);
     REQUIRE(Xq && sx, "bt_gemv_tiled_i8: NULL pointer");
     int rc = check_linear("bt_gemv_tiled_i8", M, K, tiled, N, scale, Y, y_dtype, ldy);
     if (rc) return rc;
@@ -303,7 +322,7 @@ int bt_gemv_tiled_i8(const int8_t* Xq, const float* sx, int64_t M, int64_t K, co
 
 int bt_gemv_tiled(const void* X, int x_dtype, int64_t M, int64_t K, int64_t ldx, const uint8_t* tiled, int64_t N,
                   const float* scale, const float* bias, void* Y, int y_dtype, int64_t ldy, int8_t* xq_out,
-                  float* sx_out, int32_t* acc_out, void* stream) {
+                  float* sx_out, int32_t* acc_out, int flags, void* stream) {
     REQUIRE(X != NULL, "bt_gemv_tiled: NULL pointer");
     REQUIRE(valid_dtype(x_dtype), "bt_gemv_tiled: unknown activation dtype %d", x_dtype);
     REQUIRE(ldx >= K, "bt_gemv_tiled: row stride < K");
@@ -314,7 +333,7 @@ int bt_gemv_tiled(const void* X, int x_dtype, int64_t M, int64_t K, int64_t ldx,
     int8_t* xq = (int8_t*)malloc((size_t)(M * K));
     float* sx = (float*)malloc(sizeof(float) * (size_t)M);
     act_quant_rows(x, M, K, xq, sx, NULL);
-    rc = bt_gemv_tiled_i8(xq, sx, M, K, tiled, N, scale, bias, Y, y_dtype, ldy, acc_out, stream);
+    rc = bt_gemv_tiled_i8(xq, sx, M, K, tiled, N, scale, bias, Y, y_dtype, ldy, acc_out, flags, stream);
     if (xq_out) memcpy(xq_out, xq, (size_t)(M * K));
     if (sx_out) memcpy(sx_out, sx, sizeof(float) * (size_t)M);
     free(x);
@@ -357,7 +376,7 @@ int bt_linear_unpacked(const void* X, int x_dtype, int64_t M, int64_t K, const i
                        const float* bias, void* Y, void* stream) {
     (void)stream;
     REQUIRE(X && W && scale && Y, "bt_linear_unpacked: NULL pointer");
-    REQUIRE(valid_dtype(x_dtype), "bt_linear_unpacked: unknown dtype %d", x_dtype);
+    REQUIRE(valid_dtype(x_dtype) || x_dtype == BT_F64, "bt_linear_unpacked: unknown dtype %d", x_dtype);
     REQUIRE(M > 0 && K > 0 && N > 0, "bt_linear_unpacked: X is empty");
     return float_linear(X, x_dtype, M, K, W, N, scale, bias, Y);
 }
@@ -366,7 +385,7 @@ int bt_linear_packed_float(const void* X, int x_dtype, int64_t M, int64_t K, con
                            const float* scale, const float* bias, void* Y, void* stream) {
     (void)stream;
     REQUIRE(X && packed_T && scale && Y, "bt_linear_packed_float: NULL pointer");
-    REQUIRE(valid_dtype(x_dtype), "bt_linear_packed_float: unknown dtype %d", x_dtype);
+    REQUIRE(valid_dtype(x_dtype) || x_dtype == BT_F64, "bt_linear_packed_float: unknown dtype %d", x_dtype);
     REQUIRE(M > 0 && K > 0 && N > 0, "bt_linear_packed_float: X is empty");
     int8_t* codes = (int8_t*)malloc((size_t)(N * K));
     bto_unpack_transposed(packed_T, N, K, codes);

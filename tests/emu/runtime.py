@@ -61,6 +61,7 @@ def activate() -> None:
     torch.cuda.set_device = lambda device=None: None
     torch.cuda.is_available = lambda: True
     torch.cuda.empty_cache = lambda: None
+    torch.cuda.is_current_stream_capturing = lambda: False
 
     import bittorch_b200  # noqa: F401  (loads the emulation through BITTORCH_B200_LIB)
     from bittorch_b200 import _C

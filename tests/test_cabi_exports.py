@@ -55,11 +55,16 @@ def test_argument_errors_come_back_as_codes_not_crashes():
     assert b"dtype" in lib.bt_last_error()
     assert lib.bt_quantize_pack(p(16), 0, 4, 8, 4, 0.05, None, p(16), None, None, None) == 1
     assert b"stride" in lib.bt_last_error()
-    lib.bt_gemv_tiled_i8.argtypes = [p, p, i64, i64, p, i64, p, p, p, ctypes.c_int, i64, p, p]
-    assert lib.bt_gemv_tiled_i8(p(16), p(16), 17, 64, p(16), 64, p(16), None, p(16), 0, 64, None, None) == 3  # unsupported M
+    lib.bt_gemv_tiled_i8.argtypes = [p, p, i64, i64, p, i64, p, p, p, ctypes.c_int, i64, p, ctypes.c_int, p]
+    assert lib.bt_gemv_tiled_i8(p(16), p(16), 17, 64, p(16), 64, p(16), None, p(16), 0, 64, None, 0, None) == 3  # unsupported M
     assert b"exceeds" in lib.bt_last_error()
-    assert lib.bt_gemv_tiled_i8(p(16), p(16), 0, 64, p(16), 64, p(16), None, p(16), 0, 64, None, None) == 1
+    assert lib.bt_gemv_tiled_i8(p(16), p(16), 0, 64, p(16), 64, p(16), None, p(16), 0, 64, None, 0, None) == 1
     assert b"empty" in lib.bt_last_error()
+    assert lib.bt_gemv_tiled_i8(p(16), p(16), 1, 64, p(16), 64, p(16), None, p(16), 0, 64, None, 6, None) == 1
+    assert b"flags" in lib.bt_last_error()
+    lib.bt_set_tuning.argtypes = [ctypes.c_int, ctypes.c_int]
+    assert lib.bt_set_tuning(99, 1) == 1 and b"knob" in lib.bt_last_error()
+    assert lib.bt_set_tuning(1, 128) == 0 and lib.bt_set_tuning(1, -1) == 0
     lib.bt_gemm_tiled_i8.argtypes = [p, p, p, i64, i64, p, i64, p, p, p, ctypes.c_int, i64, p, p]
     assert lib.bt_gemm_tiled_i8(p(16), p(16), p(16), 32, 40, p(16), 64, p(16), None, p(16), 0, 64, None, None) == 3
     assert b"multiple of 16" in lib.bt_last_error()

@@ -10,6 +10,8 @@ import numpy as np
 import pytest
 import torch
 
+from conftest import needs_real_gpu
+
 pytestmark = pytest.mark.gpu
 
 
@@ -115,9 +117,11 @@ def test_gemm_tcgen05_bit_exact(oracle, m, k, n):
 
 
 @pytest.mark.parametrize("bn", ["64", "128", "256"])
-def test_gemm_every_tile_width_gives_the_same_bits(oracle, bn, monkeypatch):
+def test_gemm_every_tile_width_gives_the_same_bits(oracle, bn, tuning):
     """The launcher picks the output-tile width from the problem size; force each one."""
-    monkeypatch.setenv("BITTORCH_B200_GEMM_BN", bn)
+    from bittorch_b200 import _C
+
+    tuning(_C.TUNE_GEMM_BN, int(bn))
     for (m, k, n) in [(300, 1024, 720), (17, 4096, 256), (1, 128, 16), (130, 144, 1000)]:
         prob = _problem(m, k, n, seed=int(bn) + m)
         acc_ref, y_ref = _reference(oracle, *prob)
@@ -128,9 +132,11 @@ def test_gemm_every_tile_width_gives_the_same_bits(oracle, bn, monkeypatch):
 
 @pytest.mark.parametrize("m,k,n", [(256, 128, 256), (300, 1024, 720), (129, 4096, 256), (1000, 2560, 6912),
                                    (512, 144, 1000), (2, 128, 16), (2048, 1024, 1024)])
-def test_gemm_cta_pair_kernel_bit_exact(oracle, m, k, n, monkeypatch):
+def test_gemm_cta_pair_kernel_bit_exact(oracle, m, k, n, tuning):
     """The cta_group::2 kernel (two CTAs share a 256 x 256 tile), forced for every shape."""
-    monkeypatch.setenv("BITTORCH_B200_GEMM_PAIR", "1")
+    from bittorch_b200 import _C
+
+    tuning(_C.TUNE_GEMM_PAIR, 1)
     prob = _problem(m, k, n, seed=m + 2 * k + 3 * n)
     acc_ref, y_ref = _reference(oracle, *prob)
     y, acc = _run("gemm_tiled_i8", *prob, torch.float32)
@@ -141,10 +147,12 @@ def test_gemm_cta_pair_kernel_bit_exact(oracle, m, k, n, monkeypatch):
 @pytest.mark.parametrize("split", ["1", "2", "4", "8"])
 @pytest.mark.parametrize("m,k,n", [(1, 4096, 4096), (16, 4096, 11008), (32, 2560, 6912), (5, 1024, 300), (17, 128, 256),
                                    (9, 48, 70), (20, 8192, 512), (3, 16, 5), (32, 1040, 513)])
-def test_gemm_narrow_batch_every_k_split_gives_the_same_bits(oracle, m, k, n, split, monkeypatch):
+def test_gemm_narrow_batch_every_k_split_gives_the_same_bits(oracle, m, k, n, split, tuning):
     """Up to 32 rows: full-width tiles with K split over a thread-block cluster, partial accumulators
     exchanged through distributed shared memory.  Every cluster size gives the oracle's bits."""
-    monkeypatch.setenv("BITTORCH_B200_GEMM_SPLIT", split)
+    from bittorch_b200 import _C
+
+    tuning(_C.TUNE_GEMM_SPLIT, int(split))
     prob = _problem(m, k, n, seed=int(split) + m + n)
     acc_ref, y_ref = _reference(oracle, *prob)
     y, acc = _run("gemm_tiled_i8", *prob, torch.float32)
@@ -161,6 +169,7 @@ def test_gemm_half_outputs(oracle, dtype):
     assert torch.equal(y, torch.from_numpy(y_ref).to(dtype))
 
 
+@needs_real_gpu
 def test_gemm_full_size_properties():
     """2048 x 4096 x 11008: too large for the scalar oracle in seconds, so checked through
     size-independent properties: agreement with the decode kernel on row blocks, linearity
@@ -186,6 +195,63 @@ def test_gemm_full_size_properties():
     shard = _C.retile(packed[:, 2752:5504].contiguous(), k)
     y_shard = _C.gemm_tiled_i8(xq, sx, shard, k, 2752, scale[2752:5504].contiguous(), None, torch.float32)
     assert torch.equal(y_shard, y[:, 2752:5504])
+    assert _C.device_status() == 0
+
+
+@pytest.mark.parametrize("m,k,n", [pytest.param(2048, 4096, 4096, marks=needs_real_gpu),
+                                   pytest.param(2048, 4096, 11008, marks=needs_real_gpu),
+                                   pytest.param(256, 4096, 11008, marks=needs_real_gpu), (300, 512, 320)])
+def test_gemm_config3_cells_every_row_exact(oracle, m, k, n):
+    """The config-3 prefill cells at full size, EVERY row: int32 accumulators against an exact contraction (float64
+    matmul: products <= 127 and sums <= 127 K are integers far below 2^53, so it is exact whatever the summation
+    order), outputs against the oracle's epilogue arithmetic written with separate (unfused) torch operations, and
+    a sample of rows spread over every row tile against the scalar CPU oracle itself."""
+    from bittorch_b200 import _C
+
+    g = torch.Generator().manual_seed(m + k + n)
+    codes = torch.randint(-1, 2, (n, k), generator=g, dtype=torch.int8)
+    xq = torch.randint(-127, 128, (m, k), generator=g, dtype=torch.int8)
+    sx = torch.rand(m, generator=g) * 0.05 + 1e-3
+    scale = torch.rand(n, generator=g) + 0.1
+    bias = torch.randn(n, generator=g)
+    tiled = _C.retile(_C.pack_codes(codes.cuda()), k)
+    y, acc = _C.gemm_tiled_i8(xq.cuda(), sx.cuda(), tiled, k, n, scale.cuda(), bias.cuda(), torch.float32, want_acc=True)
+    torch.cuda.synchronize()
+    assert _C.device_status() == 0
+    exact = torch.empty((m, n), dtype=torch.int32, device=acc.device)
+    cd = codes.cuda().double()
+    for m0 in range(0, m, 256):                                  # blocks of rows keep the float64 operands small
+        exact[m0:m0 + 256] = torch.matmul(xq[m0:m0 + 256].cuda().double(), cd.T).to(torch.int32)
+    assert torch.equal(acc, exact)
+    y_want = (exact.float() * sx.cuda()[:, None]) * scale.cuda()[None, :] + bias.cuda()[None, :]
+    assert torch.equal(y, y_want)
+    rows = sorted({(17 * i) % m for i in range(24)} | {0, m - 1} | set(range(127, m, 128)))[:40]
+    acc_ref = oracle.gemm_i32(xq[rows].numpy(), codes.numpy())
+    y_ref = oracle.epilogue(acc_ref, sx[rows].numpy(), scale.numpy(), bias.numpy())
+    assert np.array_equal(acc[rows].cpu().numpy(), acc_ref)
+    assert np.array_equal(y[rows].cpu().numpy().view(np.uint32), y_ref.view(np.uint32))
+
+
+def test_fresh_weights_flag_gives_the_same_bits(oracle):
+    """BT_LAUNCH_WEIGHTS_JUST_WRITTEN only changes how the decode kernel is ordered against its predecessor: the
+    re-tile, the scale conversion and the kernel enqueued back to back, results equal to the default launch."""
+    from bittorch_b200 import _C
+
+    for (m, k, n) in [(1, 4096, 1024), (3, 520, 200)]:
+        g = torch.Generator().manual_seed(m + n)
+        codes = torch.randint(-1, 2, (n, k), generator=g, dtype=torch.int8)
+        x = torch.randn(m, k, generator=g).to(torch.bfloat16).cuda()
+        scale16 = (torch.rand(n, generator=g) + 0.1).to(torch.bfloat16).cuda()
+        packed = _C.pack_codes(codes.cuda())
+        torch.cuda.synchronize()
+        tiled = _C.retile(packed, k)                              # written by the kernel just before ...
+        scale = scale16.float()                                   # ... and so is the float32 scale
+        y_fresh = _C.gemv_tiled(x, tiled, k, n, scale, None, fresh_weights=True)
+        torch.cuda.synchronize()
+        y = _C.gemv_tiled(x, tiled, k, n, scale, None)
+        xq, sx = _C.act_quant_i8(x)
+        y_i8 = _C.gemv_tiled_i8(xq, sx, tiled, k, n, scale, None, torch.bfloat16, fresh_weights=True)
+        assert torch.equal(y_fresh, y) and torch.equal(y_i8, y)
     assert _C.device_status() == 0
 
 
@@ -220,12 +286,12 @@ def test_gemv_fused_quantizer_bit_exact(oracle, m, k, n, dtype):
 
 
 @pytest.mark.parametrize("split", ["1", "2", "4", "8"])
-def test_public_layout_every_k_split_gives_the_same_bits(oracle, split, monkeypatch):
+def test_public_layout_every_k_split_gives_the_same_bits(oracle, split, tuning):
     """The compatibility kernel splits K over a thread-block cluster; every split size must
     produce the oracle's accumulators."""
     from bittorch_b200 import _C
 
-    monkeypatch.setenv("BITTORCH_B200_GEMV_SPLIT", split)
+    tuning(_C.TUNE_GEMV_SPLIT, int(split))
     for (m, k, n) in [(1, 4096, 1024), (6, 1000, 200), (16, 2048, 512)]:
         prob = _problem(m, k, n, seed=int(split) + m)
         acc_ref, y_ref = _reference(oracle, *prob)
