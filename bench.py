@@ -341,9 +341,10 @@ def launch_linear(layer: Layer, m: int, x: torch.Tensor, ldx: int, y: torch.Tens
     return 2
 
 
-def make_chain_step(layers, m: int, x0: torch.Tensor, ranks: Ranks, gather: bool = True):
+def make_chain_step(layers, m: int, x0: torch.Tensor, ranks: Ranks, gather: bool = True, published: bool = False):
     """Returns (step_fn, launches per step) for a chain of layers: the next layer reads the first K columns of the
-    previous output.  world > 1 and `gather`: each layer's [M, N/p] shard outputs are all-gathered (NCCL) into
+    previous output.  `published` (one GPU, decode kernel): every layer publishes its output rows' maxima and the
+    next layer takes its quantization scale from them (bt_gemv_tiled_chained; one memset of the maxima per step).  world > 1 and `gather`: each layer's [M, N/p] shard outputs are all-gathered (NCCL) into
     [p][M][N/p] and, for M > 1, transposed into [M, N] by one copy.  world > 1 and not `gather`: the same kernels
     with the collective taken out (each layer reads a fixed input), which is what the gathers' cost is measured
     against.  Buffers are allocated once; step_fn only enqueues."""
@@ -364,6 +365,27 @@ def make_chain_step(layers, m: int, x0: torch.Tensor, ranks: Ranks, gather: bool
         g = torch.Generator(device=dev).manual_seed(11)
         x_fixed = torch.randn(m, kmax, generator=g, device=dev).to(torch.bfloat16)
     launches = sum(1 if m <= _decode_max_m() else 2 for _ in layers)
+    if published:
+        from bittorch_b200 import _C
+        if world != 1 or m > _C.DECODE_MAX_M:
+            raise ValueError("published row maxima need the decode kernel on one GPU")
+        amax = _C.new_amax_buffer(len(layers), m, dev)
+
+    def step_published():
+        lib, st = _C._lib, _C._stream(x0)
+        amax.zero_()
+        x, ldx = x0, x0.stride(0)
+        for i, l in enumerate(layers):
+            next_k = layers[i + 1].k if i + 1 < len(layers) else l.n_local
+            _C._check(lib.bt_gemv_tiled_chained(
+                x.data_ptr(), _C.BT_BF16, m, l.k, ldx, l.tiled.data_ptr(), l.n_local, l.scale.data_ptr(), None,
+                y_loc[i].data_ptr(), _C.BT_BF16, l.n_local, amax[i - 1].data_ptr() if i > 0 else None,
+                amax[i].data_ptr(), min(next_k, l.n_local), _C.LAUNCH_DEFAULT, st))
+            x, ldx = y_loc[i], l.n_local
+        return x
+
+    if published:
+        return step_published, launches
 
     def step():
         x, ldx = x0, x0.stride(0)
@@ -391,9 +413,9 @@ def _decode_max_m() -> int:
 
 
 def time_chain(layers, m: int, x0, ranks: Ranks, gather: bool, steps: int, warmup: int, min_s: float = 0.0,
-               on_begin=None, on_end=None):
+               on_begin=None, on_end=None, published: bool = False):
     """Captures the chain and times it.  Returns dict(ms_per_step, blocks, launches_per_step, graph)."""
-    step, launches = make_chain_step(layers, m, x0, ranks, gather)
+    step, launches = make_chain_step(layers, m, x0, ranks, gather, published)
     graph, _ = capture(step)
     ms_block, blocks = time_blocks(graph.replay, steps, warmup, ranks, min_s, on_begin, on_end)
     return {"ms_per_step": ms_block / steps, "blocks": blocks, "launches_per_step": launches, "graph": graph}
@@ -778,6 +800,23 @@ def tokens_config4(dev, ranks: Ranks):
             "rows": rows, "launch": "prefill eager, decode one CUDA graph replay per token"}
 
 
+def selftest_published(dev) -> dict:
+    """The chain with published row maxima against the plain chain on a small stack: every layer's output must be
+    the same bits.  Run in a child process before the headline uses that path."""
+    from bittorch_b200 import _C
+
+    ranks = Ranks(1, 0, None, dev)
+    ok = True
+    for (k, n, count, m) in ((C3["k"], C3["k"], 3, 1), (C3["k"], C3["n"], 2, 1), (1024, 2560, 3, 4)):
+        stack = LayerStack(count, k, n, dev, seed=k + n + m)
+        x0 = torch.randn(m, k, generator=torch.Generator().manual_seed(m)).to(torch.bfloat16).to(dev)
+        plain = make_chain_step(stack.layers, m, x0, ranks, False, False)[0]().clone()
+        chained = make_chain_step(stack.layers, m, x0, ranks, False, True)[0]().clone()
+        torch.cuda.synchronize()
+        ok = ok and bool(torch.equal(plain.view(torch.int16), chained.view(torch.int16)))
+    return {"ok": ok and _C.device_status(dev) == 0}
+
+
 LEGS = ("rooflines", "config3", "tokens_config2", "tokens_config4")
 
 
@@ -788,6 +827,8 @@ def run_leg(name: str, dev, ranks: Ranks):
         return run_single_shape_rooflines(peaks, dev, ranks, traffic)
     if name == "config3":
         return run_config3(peaks, dev, ranks, traffic)
+    if name == "selftest_published":
+        return selftest_published(dev)
     if name == "tokens_config2":
         return tokens_config2(dev, ranks)
     if name == "tokens_config4":
@@ -920,11 +961,13 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--plain-chain", action="store_true",
+                    help="one GPU: do not let layers publish their row maxima (bt_gemv_tiled instead of bt_gemv_tiled_chained)")
     ap.add_argument("--no-sweep", action="store_true",
                     help="headline only: skip the single-shape rooflines, the config-3 cells, tokens/s and the CPU baseline")
     ap.add_argument("--case", default=None, choices=["gemv", "gemm", "quantize", "actquant"],
                     help="profiling aid: a few eager launches of one kernel on a small case, then exit")
-    ap.add_argument("--leg", default=None, choices=list(LEGS), help="run one secondary leg and print its result")
+    ap.add_argument("--leg", default=None, choices=list(LEGS) + ["selftest_published"], help="run one secondary leg and print its result")
     ap.add_argument("--case-m", type=int, default=None, help="rows of X for --case")
     ap.add_argument("--case-k", type=int, default=None, help="in_features for --case")
     ap.add_argument("--case-n", type=int, default=None, help="out_features for --case")
@@ -966,9 +1009,25 @@ def main() -> None:
     chain = ProjectionChain(dev, rank, world, seed=0, keep_packed=True)
     x0 = torch.randn(1, chain.layers[0].k, generator=torch.Generator().manual_seed(1)).to(torch.bfloat16).to(dev)
 
+    # One GPU: layers hand their row maxima to the next layer (bt_gemv_tiled_chained) once that path has reproduced
+    # the plain chain bit for bit in a child process on this GPU; the plain chain is timed beside it.
+    published, published_note = False, None
+    if world == 1 and not args.plain_chain:
+        res = run_leg_child("selftest_published", local_rank, 300)
+        published = res.get("ok") is True
+        if not published:
+            published_note = res.get("error", "outputs differ from the plain chain")
+    quick = {}
+    if published:                                              # a short run of each; the headline takes the faster
+        for name, flag in (("plain", False), ("published_row_maxima", True)):
+            r = time_chain(chain.layers, 1, x0, ranks, True, args.steps, args.warmup, 0.3, published=flag)
+            r.pop("graph").reset()
+            quick[name] = r["ms_per_step"]
+        published = quick["published_row_maxima"] <= quick["plain"]
+
     # ---- headline: the chain (with its all-gathers when sharded), >= MIN_TIMED_S of timed replays -------------
     head = time_chain(chain.layers, 1, x0, ranks, True, args.steps, args.warmup, MIN_TIMED_S,
-                      sampler.mark_begin, sampler.mark_end)
+                      sampler.mark_begin, sampler.mark_end, published)
     clocks, clocks_reason = sampler.stop()
     ms_per_step = head["ms_per_step"]
     job_bytes = chain_bytes(1)
@@ -987,7 +1046,7 @@ def main() -> None:
     us_launch = kern_ms * 1e3 / head["launches_per_step"]
     achieved = local_bytes / kern_ms / 1e6
     ratio, ratio_src = traffic
-    roofline = {"bound": "hbm", "kernel": "gemv_tiled_kernel<1,fused>",
+    roofline = {"bound": "hbm", "kernel": "gemv_tiled_kernel<1,fused>" + (" (row maxima published)" if published else ""),
                 "scope": f"average over the chain's {head['launches_per_step']} launches per step on one rank "
                          "(4 shapes), dependent launches, collectives taken out",
                 "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
@@ -1007,6 +1066,15 @@ def main() -> None:
            "api": "TernaryLinearInference chain" if world == 1 else "ColumnParallelTernaryLinear chain"}
 
     config = base_config(world)
+    chain_variants = None
+    if world == 1:
+        config["row_maxima"] = ("published by the producing layer (bt_gemv_tiled_chained), one memset per step"
+                                if published else "reduced by the consuming layer (bt_gemv_tiled)")
+        chain_variants = {"headline": "published_row_maxima" if published else "plain"}
+        for name, ms in quick.items():
+            chain_variants[name] = {"ms_per_step": ms, "gbs": job_bytes / ms / 1e6}
+        if published_note is not None:
+            chain_variants["published_row_maxima_not_used"] = published_note
     config["timed_region"] = (f"{head['blocks']} blocks of {args.steps} graph replays (>= {MIN_TIMED_S} s), "
                               "median block, max over ranks")
     line = {
@@ -1020,6 +1088,8 @@ def main() -> None:
     }
     if clocks is None:
         line["clocks_reason"] = clocks_reason
+    if chain_variants is not None:
+        line["chain_variants"] = chain_variants
 
     if world > 1:
         line["sharded"], graphs = sharded_section(dev, ranks, chain, args.steps, args.warmup, head)

@@ -23,6 +23,7 @@ from . import _build
 BT_F32, BT_F16, BT_BF16, BT_F64 = 0, 1, 2, 3
 LAUNCH_DEFAULT, LAUNCH_WEIGHTS_JUST_WRITTEN = 0, 1
 TUNE_GEMM_PAIR, TUNE_GEMM_BN, TUNE_GEMM_SPLIT, TUNE_GEMV_SPLIT = 0, 1, 2, 3
+AMAX_SLOTS = 8           # words per row of the row-maximum buffers of gemv_tiled_chained
 GEMV_MAX_M = 16          # largest batch the decode kernels accept
 DECODE_MAX_M = 4         # batches up to here run the decode kernel; above it the tensor-core kernel is faster
 _DT = {torch.float32: BT_F32, torch.float16: BT_F16, torch.bfloat16: BT_BF16}
@@ -53,6 +54,7 @@ _SIGNATURES = {
     "bt_gemv_packed_i8": ([_p, _p, _i64, _i64, _p, _i64, _p, _p, _p, _int, _i64, _p, _p], _int),
     "bt_gemv_tiled_i8": ([_p, _p, _i64, _i64, _p, _i64, _p, _p, _p, _int, _i64, _p, _int, _p], _int),
     "bt_gemv_tiled": ([_p, _int, _i64, _i64, _i64, _p, _i64, _p, _p, _p, _int, _i64, _p, _p, _p, _int, _p], _int),
+    "bt_gemv_tiled_chained": ([_p, _int, _i64, _i64, _i64, _p, _i64, _p, _p, _p, _int, _i64, _p, _p, _i64, _int, _p], _int),
     "bt_gemm_tiled_i8": ([_p, _p, _p, _i64, _i64, _p, _i64, _p, _p, _p, _int, _i64, _p, _p], _int),
     "bt_linear_unpacked": ([_p, _int, _i64, _i64, _p, _i64, _p, _p, _p, _p], _int),
     "bt_linear_packed_float": ([_p, _int, _i64, _i64, _p, _i64, _p, _p, _p, _p], _int),
@@ -318,6 +320,36 @@ def gemv_tiled(x2d: Tensor, tiled: Tensor, in_features: int, out_features: int, 
                                   _ptr(scale), _ptr(bias), _ptr(y), _DT[y.dtype], y.stride(0), _ptr(xq), _ptr(sx), _ptr(acc),
                                   LAUNCH_WEIGHTS_JUST_WRITTEN if fresh_weights else LAUNCH_DEFAULT, _stream(x2d)))
     return (y, xq, sx, acc) if want_debug else y
+
+
+def new_amax_buffer(layers: int, rows: int, device) -> Tensor:
+    """Zeroed row-maximum words for ``layers`` chained decode layers of ``rows`` rows each: ``buf[i]`` is what layer i
+    publishes and layer i + 1 consumes.  Zero the whole buffer (``buf.zero_()``) before every pass over the chain."""
+    return torch.zeros((layers, rows, AMAX_SLOTS), dtype=torch.int32, device=device)
+
+
+def gemv_tiled_chained(x2d: Tensor, tiled: Tensor, in_features: int, out_features: int, scale: Tensor,
+                       bias: Optional[Tensor] = None, out: Optional[Tensor] = None, amax_in: Optional[Tensor] = None,
+                       amax_out: Optional[Tensor] = None, amax_cols: Optional[int] = None,
+                       fresh_weights: bool = False) -> Tensor:
+    """``gemv_tiled`` for layers that feed one another: publishes each output row's max |y| into ``amax_out``
+    (int32 [M, AMAX_SLOTS], zero before the launch) over the leading ``amax_cols`` columns, and / or takes the
+    activation rows' maxima from ``amax_in`` (what the producer of ``x2d`` published) instead of reducing them.
+    Bit-identical to ``gemv_tiled``."""
+    if x2d.stride(1) != 1:
+        raise RuntimeError("gemv_tiled_chained: activation rows must be contiguous (the producer's layout)")
+    m = x2d.shape[0]
+    y = torch.empty((m, out_features), dtype=x2d.dtype, device=x2d.device) if out is None else out
+    for name, buf in (("amax_in", amax_in), ("amax_out", amax_out)):
+        if buf is not None and (buf.dtype != torch.int32 or tuple(buf.shape) != (m, AMAX_SLOTS) or not buf.is_contiguous()):
+            raise RuntimeError(f"gemv_tiled_chained: {name} must be a contiguous int32 [{m}, {AMAX_SLOTS}] tensor")
+    cols = out_features if amax_cols is None else int(amax_cols)
+    with torch.cuda.device(x2d.device):
+        _check(_lib.bt_gemv_tiled_chained(_ptr(x2d), _dtype_code(x2d, "X"), m, in_features, x2d.stride(0), _ptr(tiled),
+                                          out_features, _ptr(scale), _ptr(bias), _ptr(y), _DT[y.dtype], y.stride(0),
+                                          _ptr(amax_in), _ptr(amax_out), cols,
+                                          LAUNCH_WEIGHTS_JUST_WRITTEN if fresh_weights else LAUNCH_DEFAULT, _stream(x2d)))
+    return y
 
 
 def gemm_tiled_i8(xq, sx, tiled, in_features, out_features, scale, bias=None, out_dtype=torch.float32, want_acc=False,

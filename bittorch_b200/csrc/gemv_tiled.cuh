@@ -18,6 +18,14 @@
 // adds the 16 warps' slots, subtracts the row sum of the activations that met planes 0..2
 // (whose codes are stored as t+1) and applies (float(acc) * sx) * scale + bias.
 //
+// Chained layers (bt_gemv_tiled_chained): when this kernel's output rows are the next layer's activations, the
+// epilogue also publishes each row's max |y| (of the values as stored, i.e. after rounding to the output type, over
+// the columns the next layer reads): one atomicMax on the float's bit pattern per CTA and row into one of
+// AMAX_SLOTS words.  The next layer then takes its quantization scale from those words instead of reducing the row
+// itself, so its threads quantize their share of the row as soon as it arrives: no row-maximum pass and no CTA
+// barrier between the activation load and the quantizer.  Bit-identical by construction: the maximum is taken over
+// exactly the values the consumer would have reduced.
+//
 // Algorithmic HBM bytes per call: ceil(K/4)*N + 4N (+4N bias) + x + y.
 #pragma once
 
@@ -37,6 +45,7 @@ constexpr int GT_MAX_STAGES = 3;                       // up to 96 KB of weights
 constexpr int GT_MAX_ROWS = 8;                         // activation rows per launch (accumulators live in registers)
 constexpr int GT_X_PAD = 16;                           // bytes of padding per activation row in shared memory
 constexpr int GT_SLOT_BUDGET = 32;                     // column blocks per CTA x padded rows, bounds the partial-sum slots
+constexpr int AMAX_SLOTS = BT_AMAX_SLOTS;              // words per row that share the row-maximum atomics of a launch
 
 struct GemvTiledParams {
     const void* X;         // FUSED: floating-point activations [M,K], row stride ldx
@@ -58,6 +67,9 @@ struct GemvTiledParams {
     int x_dtype, y_dtype;
     int x_vec;             // activation rows can be read with vector loads
     int serialized;        // host only: launch without programmatic dependent launch (weights were just written)
+    const uint32_t* amax_in;   // FUSED, optional: [M][AMAX_SLOTS] bit patterns whose maximum is the row's max |x|
+    uint32_t* amax_out;        // optional: [M][AMAX_SLOTS], receives max |y as stored| over columns < amax_cols
+    int amax_cols;
 };
 
 // Loads 4 consecutive activations of runtime dtype as float.
@@ -65,6 +77,13 @@ __device__ __forceinline__ void load_x4(const void* X, int dtype, int64_t idx, b
     if (dtype == BT_BF16) load4<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(X) + idx, vec, valid, out);
     else if (dtype == BT_F16) load4<__half>(static_cast<const __half*>(X) + idx, vec, valid, out);
     else load4<float>(static_cast<const float*>(X) + idx, vec, valid, out);
+}
+
+// The value a consumer reads back after `y` was stored as `dtype`.
+__device__ __forceinline__ float rounded_as_stored(float y, int dtype) {
+    if (dtype == BT_BF16) return round_through<__nv_bfloat16>(y);
+    if (dtype == BT_F16) return round_through<__half>(y);
+    return y;
 }
 
 // Two CTAs per SM (<= 56 registers) for the small row counts, so that the next layer's CTAs
@@ -87,6 +106,7 @@ gemv_tiled_kernel(const GemvTiledParams p) {
     uint64_t* s_full = reinterpret_cast<uint64_t*>((reinterpret_cast<uintptr_t>(s_bias + p.nbl_max * TILE_N) + 7) & ~uintptr_t(7));
     uint64_t* s_empty = s_full + p.stages;
     __shared__ int s_abort;
+    __shared__ uint32_t s_amax[GT_MAX_ROWS];               // this CTA's max |y| per row (bit patterns), amax_out only
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int stages = p.stages;
@@ -106,6 +126,7 @@ gemv_tiled_kernel(const GemvTiledParams p) {
         s_abort = 0;
         mbar_fence_init();
     }
+    if (tid < GT_MAX_ROWS) s_amax[tid] = 0u;
     for (int i = tid; i < GT_CONSUMER_WARPS * p.nbl_max * TILE_N * MR + MR + 2 * GT_CONSUMER_WARPS * MR; i += GT_THREADS)
         s_part[i] = 0;                                  // s_part, s_rowsum, s_wsum, s_wmax (0.0f)
     for (int c = tid; c < nbl * TILE_N; c += GT_THREADS) {   // epilogue constants: never written by a preceding kernel
@@ -148,9 +169,20 @@ gemv_tiled_kernel(const GemvTiledParams p) {
             const int64_t row_off = static_cast<int64_t>(m) * p.ldx;
             // a row that fits four vectors per thread stays in registers between the two passes
             const bool single = nvec <= 4 * tpr;
+            // the producing kernel published the row maxima: no reduction pass, no barrier before the quantizer
+            const bool published = p.amax_in != nullptr;
+            uint32_t pub = 0u;
+            if (published && row_ok) {
+                const uint4* words = reinterpret_cast<const uint4*>(p.amax_in + static_cast<int64_t>(m) * AMAX_SLOTS);
+#pragma unroll
+                for (int q = 0; q < AMAX_SLOTS / 4; ++q) {
+                    const uint4 w = __ldcg(words + q);
+                    pub = max(max(pub, max(w.x, w.y)), max(w.z, w.w));
+                }
+            }
             float x[4][4];
             float mx = 0.0f;
-            if (row_ok) {
+            if (row_ok && (single || !published)) {
                 for (int v0 = j; v0 < nvec; v0 += 4 * tpr) {
 #pragma unroll
                     for (int u = 0; u < 4; ++u) {           // four independent loads in flight
@@ -164,12 +196,16 @@ gemv_tiled_kernel(const GemvTiledParams p) {
                         mx = fmaxf(fmaxf(fmaxf(mx, fabsf(x[u][0])), fmaxf(fabsf(x[u][1]), fabsf(x[u][2]))), fabsf(x[u][3]));
                 }
             }
-            mx = warp_max(mx);                              // a warp never straddles two rows (tpr >= 64)
-            if (lane == 0 && row_ok) s_wmax[warp * MR + m] = mx;
-            asm volatile("bar.sync 1, %0;" ::"r"(GT_NCONS) : "memory");
             float amax = 0.0f;
+            if (published) {                                // the same condition in every thread of the CTA
+                amax = __uint_as_float(pub);
+            } else {
+                mx = warp_max(mx);                          // a warp never straddles two rows (tpr >= 64)
+                if (lane == 0 && row_ok) s_wmax[warp * MR + m] = mx;
+                asm volatile("bar.sync 1, %0;" ::"r"(GT_NCONS) : "memory");
 #pragma unroll
-            for (int w = 0; w < GT_CONSUMER_WARPS; ++w) amax = fmaxf(amax, s_wmax[w * MR + (row_ok ? m : 0)]);
+                for (int w = 0; w < GT_CONSUMER_WARPS; ++w) amax = fmaxf(amax, s_wmax[w * MR + (row_ok ? m : 0)]);
+            }
             // csrc/kernels/ternary_gemm_tensor_core.cu:438-440 (scale rule) and :456 (reciprocal)
             const float sxm = (amax > 1e-6f) ? __fdiv_rn(amax, 127.0f) : 1.0f;
             const float inv = __fdiv_rn(1.0f, sxm);
@@ -372,7 +408,9 @@ gemv_tiled_kernel(const GemvTiledParams p) {
     }
     // epilogue: one thread per (row, column) of this CTA's column blocks, columns fastest
     const int cols = nbl * TILE_N;
-    for (int m = 0; m < p.M; ++m)
+    const bool publish = p.amax_out != nullptr;
+    for (int m = 0; m < p.M; ++m) {
+        float ymax = 0.0f;
         for (int c = tid; c < cols; c += GT_THREADS) {
             const int n = nb0 * TILE_N + c;
             if (n >= p.N) continue;
@@ -382,7 +420,20 @@ gemv_tiled_kernel(const GemvTiledParams p) {
             if (p.acc_out != nullptr) p.acc_out[static_cast<int64_t>(m) * p.N + n] = acc;
             const float y = dequant(acc, s_sx[m], s_scale[c], s_bias[c], p.bias != nullptr);
             store_out_dt(p.Y, p.y_dtype, static_cast<int64_t>(m) * p.ldy + n, y);
+            // fmaxf drops a NaN operand, as the consumer's own reduction does
+            if (publish && n < p.amax_cols) ymax = fmaxf(ymax, fabsf(rounded_as_stored(y, p.y_dtype)));
         }
+        if (publish) {                                      // the same condition in every thread: whole warps get here
+            ymax = warp_max(ymax);
+            if (lane == 0 && ymax > 0.0f) atomicMax(&s_amax[m], __float_as_uint(ymax));
+        }
+    }
+    if (publish) {
+        __syncthreads();
+        // non-negative floats order like their bit patterns; CTAs spread over AMAX_SLOTS words per row
+        if (tid < p.M && s_amax[tid] != 0u)
+            atomicMax(p.amax_out + static_cast<int64_t>(tid) * AMAX_SLOTS + (blockIdx.x % AMAX_SLOTS), s_amax[tid]);
+    }
 }
 
 // ---- host side ------------------------------------------------------------------------------
@@ -461,6 +512,8 @@ static int launch_gemv_tiled(const GemvTiledParams& p, cudaStream_t st) {
         if (p.xq_out != nullptr) q.xq_out = p.xq_out + static_cast<int64_t>(m0) * p.K;
         if (p.sx_out != nullptr) q.sx_out = p.sx_out + m0;
         if (p.acc_out != nullptr) q.acc_out = p.acc_out + static_cast<int64_t>(m0) * p.N;
+        if (p.amax_in != nullptr) q.amax_in = p.amax_in + static_cast<int64_t>(m0) * AMAX_SLOTS;
+        if (p.amax_out != nullptr) q.amax_out = p.amax_out + static_cast<int64_t>(m0) * AMAX_SLOTS;
         q.Y = static_cast<char*>(p.Y) + static_cast<size_t>(m0) * p.ldy * dtype_size(p.y_dtype);
         const int rc = launch_gemv_tiled_rows(q, st);
         if (rc != BT_OK) return rc;
@@ -520,5 +573,26 @@ extern "C" int bt_gemv_tiled(const void* X, int x_dtype, int64_t M, int64_t K, i
     GemvTiledParams p = base_tiled_params(M, K, tiled, N, scale, bias, Y, y_dtype, ldy, acc_out, flags);
     p.X = X; p.x_dtype = x_dtype; p.ldx = ldx; p.xq_out = xq_out; p.sx_out = sx_out;
     p.x_vec = (K % 4 == 0) && (ldx % 4 == 0) && aligned(X, 4 * dtype_size(x_dtype));
+    return launch_gemv_tiled(p, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int bt_gemv_tiled_chained(const void* X, int x_dtype, int64_t M, int64_t K, int64_t ldx, const uint8_t* tiled,
+                                     int64_t N, const float* scale, const float* bias, void* Y, int y_dtype, int64_t ldy,
+                                     const uint32_t* amax_in, uint32_t* amax_out, int64_t amax_cols, int flags,
+                                     void* stream) {
+    using namespace bt;
+    BT_REQUIRE(X != nullptr, "bt_gemv_tiled_chained: NULL pointer");
+    BT_REQUIRE((flags & ~BT_LAUNCH_WEIGHTS_JUST_WRITTEN) == 0, "bt_gemv_tiled_chained: unknown flags %d", flags);
+    BT_REQUIRE(valid_dtype(x_dtype), "bt_gemv_tiled_chained: unknown activation dtype %d", x_dtype);
+    BT_REQUIRE(ldx >= K, "bt_gemv_tiled_chained: row stride %lld < K %lld", (long long)ldx, (long long)K);
+    BT_REQUIRE(amax_in == nullptr || aligned(amax_in, 16), "bt_gemv_tiled_chained: amax_in must be 16-byte aligned");
+    BT_REQUIRE(amax_out == nullptr || (amax_cols > 0 && amax_cols <= N),
+               "bt_gemv_tiled_chained: amax_cols %lld outside 1..N", (long long)amax_cols);
+    int rc = check_gemv_tiled_args("bt_gemv_tiled_chained", M, K, tiled, N, scale, Y, y_dtype, ldy);
+    if (rc != BT_OK) return rc;
+    GemvTiledParams p = base_tiled_params(M, K, tiled, N, scale, bias, Y, y_dtype, ldy, nullptr, flags);
+    p.X = X; p.x_dtype = x_dtype; p.ldx = ldx;
+    p.x_vec = (K % 4 == 0) && (ldx % 4 == 0) && aligned(X, 4 * dtype_size(x_dtype));
+    p.amax_in = amax_in; p.amax_out = amax_out; p.amax_cols = static_cast<int>(amax_cols);
     return launch_gemv_tiled(p, static_cast<cudaStream_t>(stream));
 }

@@ -69,6 +69,8 @@ extern "C" {
 
 /* Largest M handled by the decode (GEMV) kernels. */
 #define BT_GEMV_MAX_M 16
+/* Words per row of the row-maximum buffers of bt_gemv_tiled_chained. */
+#define BT_AMAX_SLOTS 8
 /* Largest K of the integer kernels: keeps 128*127*K inside int32. */
 #define BT_MAX_K 131072
 
@@ -207,6 +209,32 @@ int bt_gemv_tiled(const void* X, int x_dtype, int64_t M, int64_t K, int64_t ldx,
                   const uint8_t* tiled, int64_t N, const float* scale, const float* bias,
                   void* Y, int y_dtype, int64_t ldy, int8_t* xq_out, float* sx_out,
                   int32_t* acc_out, int flags, void* stream);
+
+/*
+ * bt_gemv_tiled for layers that feed one another: the kernel that WRITES a layer's
+ * activations also publishes each row's max |y|, so the kernel that READS them takes its
+ * per-token quantization scale from there instead of reducing the row first (no
+ * row-maximum pass and no block-wide barrier in front of the quantizer).  Results are
+ * bit-identical to bt_gemv_tiled: the maximum is taken over the values as stored in
+ * y_dtype, which are the values the consumer would have reduced.
+ * (No counterpart in the reference, whose integer kernel re-derives the scale inside
+ * every tile: csrc/kernels/ternary_gemm_tensor_core.cu:424-444.)
+ *
+ * amax_out  uint32 [M][BT_AMAX_SLOTS] or NULL: receives, by atomic maximum on the float
+ *           bit patterns, max |Y[m, 0..amax_cols)| spread over the BT_AMAX_SLOTS words of
+ *           row m (their maximum is the row's value).  MUST BE ZERO before the launch
+ *           (one memset for all layers of a step); amax_cols = the leading columns the
+ *           consumer reads (its K).
+ * amax_in   uint32 [M][BT_AMAX_SLOTS] or NULL, 16-byte aligned: what the producer of X
+ *           published.  Preconditions: that producer stored exactly this call's
+ *           X[0..M, 0..K) in x_dtype with amax_cols == K, and nothing modified X since.
+ *           With NULL the kernel reduces the rows itself, like bt_gemv_tiled.
+ * Other arguments and `flags` as bt_gemv_tiled (no debug outputs).
+ */
+int bt_gemv_tiled_chained(const void* X, int x_dtype, int64_t M, int64_t K, int64_t ldx,
+                          const uint8_t* tiled, int64_t N, const float* scale, const float* bias,
+                          void* Y, int y_dtype, int64_t ldy, const uint32_t* amax_in,
+                          uint32_t* amax_out, int64_t amax_cols, int flags, void* stream);
 
 /*
  * Prefill-size packed ternary linear on int8 activations (any M >= 1), same

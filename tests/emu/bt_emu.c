@@ -342,6 +342,61 @@ int bt_gemv_tiled(const void* X, int x_dtype, int64_t M, int64_t K, int64_t ldx,
     return rc;
 }
 
+/* Quantizer of bto_act_quant with the row maximum supplied from outside. */
+static void quantize_row_with_max(const float* row, int64_t K, float mx, int8_t* q, float* sx) {
+    float s = (mx > 1e-6f) ? (mx / 127.0f) : 1.0f;
+    float inv = 1.0f / s;
+    *sx = s;
+    for (int64_t k = 0; k < K; ++k) {
+        float v = fmaxf(-127.0f, fminf(127.0f, roundf(row[k] * inv)));
+        q[k] = (int8_t)v;
+    }
+}
+
+int bt_gemv_tiled_chained(const void* X, int x_dtype, int64_t M, int64_t K, int64_t ldx, const uint8_t* tiled, int64_t N,
+                          const float* scale, const float* bias, void* Y, int y_dtype, int64_t ldy,
+                          const uint32_t* amax_in, uint32_t* amax_out, int64_t amax_cols, int flags, void* stream) {
+    REQUIRE(X != NULL, "bt_gemv_tiled_chained: NULL pointer");
+    REQUIRE((flags & ~BT_LAUNCH_WEIGHTS_JUST_WRITTEN) == 0, "bt_gemv_tiled_chained: unknown flags %d", flags);
+    REQUIRE(valid_dtype(x_dtype), "bt_gemv_tiled_chained: unknown activation dtype %d", x_dtype);
+    REQUIRE(ldx >= K, "bt_gemv_tiled_chained: row stride < K");
+    REQUIRE(amax_in == NULL || ((uintptr_t)amax_in % 16) == 0, "bt_gemv_tiled_chained: amax_in must be 16-byte aligned");
+    REQUIRE(amax_out == NULL || (amax_cols > 0 && amax_cols <= N), "bt_gemv_tiled_chained: amax_cols outside 1..N");
+    int rc = check_linear("bt_gemv_tiled_chained", M, K, tiled, N, scale, Y, y_dtype, ldy);
+    if (rc) return rc;
+    if (M > BT_GEMV_MAX_M) return fail(BT_ERR_UNSUPPORTED, "bt_gemv_tiled_chained: M=%lld exceeds %d", (long long)M, BT_GEMV_MAX_M);
+    float* x = widen(X, x_dtype, M, K, ldx);
+    int8_t* xq = (int8_t*)malloc((size_t)(M * K));
+    float* sx = (float*)malloc(sizeof(float) * (size_t)M);
+    if (amax_in) {
+        for (int64_t m = 0; m < M; ++m) {
+            uint32_t best = 0;
+            for (int s = 0; s < BT_AMAX_SLOTS; ++s)
+                if (amax_in[m * BT_AMAX_SLOTS + s] > best) best = amax_in[m * BT_AMAX_SLOTS + s];
+            float mx;
+            memcpy(&mx, &best, 4);
+            quantize_row_with_max(x + m * K, K, mx, xq + m * K, sx + m);
+        }
+    } else {
+        act_quant_rows(x, M, K, xq, sx, NULL);
+    }
+    rc = bt_gemv_tiled_i8(xq, sx, M, K, tiled, N, scale, bias, Y, y_dtype, ldy, NULL, flags, stream);
+    if (rc == BT_OK && amax_out) {
+        for (int64_t m = 0; m < M; ++m) {
+            float mx = 0.0f;
+            for (int64_t n = 0; n < amax_cols; ++n) mx = fmaxf(mx, fabsf(load_elem(Y, y_dtype, m * ldy + n)));
+            uint32_t bits;
+            memcpy(&bits, &mx, 4);
+            uint32_t* slot = amax_out + m * BT_AMAX_SLOTS + (3 * m + 5) % BT_AMAX_SLOTS;     /* any slot of the row */
+            if (bits > *slot) *slot = bits;
+        }
+    }
+    free(x);
+    free(xq);
+    free(sx);
+    return rc;
+}
+
 int bt_gemm_tiled_i8(const int8_t* Xq, const float* sx, const int32_t* xsum, int64_t M, int64_t K, const uint8_t* tiled,
                      int64_t N, const float* scale, const float* bias, void* Y, int y_dtype, int64_t ldy,
                      int32_t* acc_out, void* stream) {

@@ -36,6 +36,8 @@ def test_one_gpu_line_has_every_contract_key_and_every_leg():
     c = d["clocks"]
     assert c["samples"] >= 3 and c["window"] == "timed region" and c["reasons"] == ["sw_power_cap"]
     assert d["device_status"] == 0
+    v = d["chain_variants"]                                     # both chains were timed; the headline is one of them
+    assert v["headline"] in ("plain", "published_row_maxima") and v["plain"]["gbs"] > 0 and v["published_row_maxima"]["gbs"] > 0
     assert not [k for k in d if k.endswith("_error")], [d[k] for k in d if k.endswith("_error")]
     assert len(d["rooflines"]) == 3 and all(x["frac"] > 0 for x in d["rooflines"])
     g = d["roofline_gemm"]

@@ -330,3 +330,59 @@ def test_gemv_fused_strided_rows(oracle):
     q_ref, sx_ref = oracle.act_quant(x.float().cpu().numpy())
     assert np.array_equal(xq.cpu().numpy(), q_ref)
     assert np.array_equal(acc.cpu().numpy(), oracle.gemm_i32(q_ref, codes.numpy()))
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("m", [1, 3, 8, 11])
+def test_chained_layers_with_published_row_maxima_give_the_same_bits(oracle, m, dtype):
+    """Three layers in a row, each reading the leading K columns of the previous output: with the row maxima
+    published by the producing kernel (bt_gemv_tiled_chained) every output equals the plain kernels', bit for bit -
+    ragged shapes, a row of zeros (scale rule's 1e-6 branch), an infinite value, more output columns than the next
+    layer reads."""
+    from bittorch_b200 import _C
+
+    shapes = [(200, 520), (264, 330), (330, 96)]                 # (K, N); the next K is smaller than this N
+    g = torch.Generator().manual_seed(100 * m + len(str(dtype)))
+    layers = []
+    for k, n in shapes:
+        codes = torch.randint(-1, 2, (n, k), generator=g, dtype=torch.int8)
+        scale = (torch.rand(n, generator=g) * 0.02 + 0.001).cuda()
+        bias = (torch.randn(n, generator=g) * 0.01).cuda()
+        layers.append((k, n, _C.retile(_C.pack_codes(codes.cuda()), k), scale, bias))
+    x0 = torch.randn(m, 200, generator=g).to(dtype)
+    if m >= 3:
+        x0[1] = 0                                                 # max |x| <= 1e-6: scale 1
+    if m >= 8:
+        x0[5, 17] = float("inf")
+    x0 = x0.cuda()
+    torch.cuda.synchronize()
+
+    def run(chained):
+        amax = _C.new_amax_buffer(len(layers), m, x0.device)
+        x, outs = x0, []
+        for i, (k, n, tiled, scale, bias) in enumerate(layers):
+            xin = x[:, :k]
+            if chained:
+                next_k = layers[i + 1][0] if i + 1 < len(layers) else n
+                y = _C.gemv_tiled_chained(xin, tiled, k, n, scale, bias, amax_in=amax[i - 1] if i > 0 else None,
+                                          amax_out=amax[i], amax_cols=next_k)
+            else:
+                y = _C.gemv_tiled(xin, tiled, k, n, scale, bias)
+            outs.append(y)
+            x = y
+        torch.cuda.synchronize()
+        return outs, amax
+
+    plain, _ = run(False)
+    chained, amax = run(True)
+    for a, b in zip(plain, chained):
+        assert torch.equal(a.view(torch.int16 if a.element_size() == 2 else torch.int32),
+                           b.view(torch.int16 if b.element_size() == 2 else torch.int32))
+    # what was published is the maximum of the stored values over the columns the next layer reads
+    for i, y in enumerate(chained):
+        next_k = layers[i + 1][0] if i + 1 < len(layers) else layers[i][1]
+        vals = y[:, :next_k].float().abs()
+        want = torch.where(torch.isnan(vals), torch.zeros_like(vals), vals).max(dim=1).values
+        got = amax[i].max(dim=1).values.view(torch.float32) if amax[i].dtype == torch.int32 else None
+        assert torch.equal(got.cpu(), want.cpu())
+    assert _C.device_status() == 0

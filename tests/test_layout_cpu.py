@@ -137,3 +137,35 @@ def test_k_split_of_the_narrow_batch_gemm_covers_every_block_once():
         owners = [(c0 // cols_own, c0 % cols_own) for c0 in range(0, 256, 32)]
         assert sorted(set(o for o, _ in owners)) == list(range(s))
         assert all(off + 32 <= cols_own for _, off in owners)
+
+
+def test_a_published_row_maximum_is_the_maximum_the_consumer_would_reduce():
+    """Chained decode layers: the producer publishes max |y as stored| by an atomic maximum on float BIT PATTERNS,
+    the consumer turns the winning pattern back into a float and derives its scale from it.  For the result to be
+    bit-identical to the consumer reducing the row itself, (1) non-negative floats must order like their unsigned
+    bit patterns, infinities included, (2) the maximum must be taken over the values after rounding to the storage
+    type, and (3) NaN must be dropped the way fmaxf drops it.  Checked here with numpy on bf16 / fp16 / fp32 storage."""
+    import torch
+
+    rng = np.random.default_rng(5)
+    for dtype in (torch.bfloat16, torch.float16, torch.float32):
+        for trial in range(20):
+            y = torch.from_numpy((rng.standard_normal(300) * 10.0 ** rng.integers(-6, 5)).astype(np.float32))
+            if trial % 5 == 1:
+                y[7] = float("inf")
+            if trial % 5 == 2:
+                y[3], y[11] = float("nan"), -0.0
+            stored = y.to(dtype).float()                               # what the consumer reads back
+            clean = torch.where(torch.isnan(stored), torch.zeros_like(stored), stored.abs())
+            want = float(clean.max())                                  # fmaxf-style reduction: NaN dropped
+            bits = clean.numpy().view(np.uint32)
+            got = np.array([bits.max()], dtype=np.uint32).view(np.float32)[0]
+            assert got == want or (np.isinf(got) and np.isinf(want))
+            order = np.argsort(clean.numpy(), kind="stable")
+            assert np.all(np.diff(bits[order].astype(np.int64)) >= 0)  # value order == bit-pattern order
+    # spread over slots: the row's value is the maximum of its slots, zero slots are neutral
+    slots = np.zeros(8, dtype=np.uint32)
+    for v in (0.5, 3.25, 1e-9):
+        s = rng.integers(0, 8)
+        slots[s] = max(slots[s], np.array([v], np.float32).view(np.uint32)[0])
+    assert slots.max().view(np.float32) == np.float32(3.25)
