@@ -4,7 +4,9 @@
 Buffers keep the reference's names, dtypes and shapes (``weight_packed`` uint8
 [ceil(K/4), N], ``scale`` [N], ``bias`` [N]) so its checkpoints load unchanged.  The
 forward runs on a privately re-tiled copy of ``weight_packed`` that is rebuilt whenever
-the buffer changes and is never serialized.
+the buffer changes and is never serialized.  ``compact()`` drops the public buffer from the
+device once the tiled copy exists (one copy of the weights, 2 bits each); ``state_dict()`` then
+rebuilds ``weight_packed`` from the tiled copy, byte for byte, so checkpoints do not change.
 """
 
 from __future__ import annotations
@@ -36,6 +38,8 @@ class TernaryLinearInference(nn.Module):
         self._tiled: Optional[Tensor] = None
         self._scale32: Optional[Tensor] = None
         self._bias32: Optional[Tensor] = None
+        self._compact = False                                  # True: weight_packed is an empty placeholder
+        self._register_state_dict_hook(_packed_into_state_dict)
 
     # Check the buffers' contents (a sampled fingerprint, one host synchronisation per forward) next to their
     # addresses and version counters, so that a write through ``weight_packed.data`` / ``scale.data`` is seen.
@@ -46,9 +50,34 @@ class TernaryLinearInference(nn.Module):
         """Rebuild the derived buffers (tiled weights, float32 scale / bias) on the next forward."""
         self._derived_key = None
 
-    def _load_from_state_dict(self, *args, **kwargs):
+    def _load_from_state_dict(self, state_dict, prefix, *args, **kwargs):
+        if self._compact:                                      # make room for the incoming public buffer
+            self.weight_packed = torch.empty(((self.in_features + 3) // 4, self.out_features), dtype=torch.uint8,
+                                             device=self.scale.device)
+            self._compact = False
+            self._tiled = None
         self.invalidate_cache()
-        return super()._load_from_state_dict(*args, **kwargs)
+        return super()._load_from_state_dict(state_dict, prefix, *args, **kwargs)
+
+    def compact(self, tiled: Optional[Tensor] = None) -> "TernaryLinearInference":
+        """Keep ONE device copy of the weights: the tiled buffer the kernels read.  The public ``weight_packed``
+        buffer is released (the attribute becomes an empty placeholder); ``state_dict()`` and ``public_packed()``
+        rebuild it from the tiled copy with ``bt_untile_packed``, bit for bit.  ``tiled``: adopt this buffer (e.g. a
+        view into a larger one shared with sibling layers) instead of re-tiling.  Undone by ``load_state_dict``."""
+        if not self._compact:
+            if tiled is None:
+                tiled = self._derived()[0]
+            self._tiled = tiled
+            self.weight_packed = torch.empty(0, dtype=torch.uint8, device=self.scale.device)
+            self._compact = True
+            self._derived_key = None
+        return self
+
+    def public_packed(self) -> Tensor:
+        """The wire-format buffer uint8 [ceil(K/4), N], whether or not the module still holds it."""
+        if not self._compact:
+            return self.weight_packed
+        return require_ext().untile(self._tiled, self.in_features, self.out_features)
 
     def _derived(self):
         """(tiled weights, float32 scale, float32 bias, fresh): rebuilt when a buffer was replaced or written;
@@ -56,16 +85,18 @@ class TernaryLinearInference(nn.Module):
         from .ternary_linear_cuda import capturing, content_fingerprint
 
         wp, sc, b = self.weight_packed, self.scale, self.bias
-        key = (wp.data_ptr(), wp._version, sc.data_ptr(), sc._version,
-               None if b is None else (b.data_ptr(), b._version))
+        watched = (sc,) if self._compact else (wp, sc)          # a compact module has no public buffer to watch
+        key = tuple(v for t in watched for v in (t.data_ptr(), t._version)) + (
+            None if b is None else (b.data_ptr(), b._version),)
         if self.verify_buffers and not capturing():
-            key += content_fingerprint(wp, sc, *(() if b is None else (b,)))
+            key += content_fingerprint(*watched, *(() if b is None else (b,)))
         elif self._derived_key is not None:
             key += self._derived_key[len(key):]                # keep comparing addresses and versions only
         fresh = key != self._derived_key
         if fresh:
             C = require_ext()
-            self._tiled = C.retile(wp, self.in_features)
+            if not self._compact:
+                self._tiled = C.retile(wp, self.in_features)
             self._scale32 = sc.to(torch.float32).contiguous()
             self._bias32 = None if b is None else b.to(torch.float32).contiguous()
             self._derived_key = key
@@ -80,14 +111,14 @@ class TernaryLinearInference(nn.Module):
         if x.numel() == 0:
             raise RuntimeError("X is empty")
         if C.activation_mode() == "float" or x.dtype == torch.float64:
-            return C.ternary_linear_packed_forward(x, self.weight_packed, self.scale, self.bias, self.in_features)
+            return C.ternary_linear_packed_forward(x, self.public_packed(), self.scale, self.bias, self.in_features)
         tiled, s32, b32, fresh = self._derived()
         x2d = x.contiguous().reshape(-1, self.in_features)
         y = C.int8_linear_tiled(x2d, tiled, self.in_features, self.out_features, s32, b32, fresh_weights=fresh)
         return y.reshape(*x.shape[:-1], self.out_features)
 
     def extra_repr(self) -> str:
-        packed_bytes = self.weight_packed.numel()
+        packed_bytes = self.packed_size_bytes
         reduction = (self.out_features * self.in_features * 4) / (packed_bytes + self.scale.numel() * 2)
         return (f"in_features={self.in_features}, out_features={self.out_features}, bias={self.bias is not None}, "
                 f"packed_bytes={packed_bytes}, reduction={reduction:.1f}x")
@@ -102,12 +133,19 @@ class TernaryLinearInference(nn.Module):
 
     @property
     def packed_size_bytes(self) -> int:
-        return self.weight_packed.numel()
+        return ((self.in_features + 3) // 4) * self.out_features
 
     @property
     def effective_bits_per_weight(self) -> float:
-        total_bits = self.weight_packed.numel() * 8 + self.scale.numel() * 16
+        total_bits = self.packed_size_bytes * 8 + self.scale.numel() * 16
         return total_bits / (self.out_features * self.in_features)
+
+
+def _packed_into_state_dict(module, state_dict, prefix, local_metadata):
+    """state_dict hook: a compact module serializes the public buffer rebuilt from its tiled copy."""
+    if module._compact:
+        state_dict[prefix + "weight_packed"] = module.public_packed()
+    return state_dict
 
 
 def create_ternary_linear_inference(in_features: int, out_features: int, weight: Tensor, bias: Optional[Tensor] = None,

@@ -55,6 +55,7 @@ class DecoderConfig:
     n_kv_heads: Optional[int] = None          # defaults to n_heads (TernaryTransformer.ts:116)
     threshold_factor: float = 0.05
     backend: str = "auto"
+    one_weight_copy: bool = True              # inference form: keep only the tiled copy of every projection on the device
 
     def __post_init__(self) -> None:
         if self.n_kv_heads is None:
@@ -107,20 +108,40 @@ def apply_rope_at(x: Tensor, cos: Tensor, sin: Tensor, pos: Tensor) -> Tensor:
     return torch.cat([x0 * c - x1 * s, x0 * s + x1 * c], dim=-1)
 
 
-def fuse_inference_columns(layers) -> TernaryLinearInference:
+def fuse_inference_columns(layers, share: bool = False) -> TernaryLinearInference:
     """Packed layers that read the same input, as ONE layer with their output columns side by side.  Columns of a
     packed ternary layer are independent (own bytes, own scale; the activation quantizer depends on the input
     only), so the fused layer's outputs are the members' outputs concatenated, bit for bit - and a decode step
-    pays one dependent kernel launch instead of one per member."""
+    pays one dependent kernel launch instead of one per member.
+
+    ``share`` (every member's width a multiple of the 16-column tile): the fused layer and its members end up
+    with ONE device copy of the weights between them.  The tiled layout is column-block major, so the fused tiled
+    buffer is the members' tiled buffers one after the other; the members become compact modules whose tiled
+    buffers are views into it, and nobody keeps a public packed buffer (state dicts rebuild it)."""
     k = layers[0].in_features
     if any(l.in_features != k for l in layers):
         raise ValueError("fused layers must read the same input")
-    wp = torch.cat([l.weight_packed for l in layers], dim=1).contiguous()
     scale = torch.cat([l.scale for l in layers])
     bias = None
     if any(l.bias is not None for l in layers):
         bias = torch.cat([l.bias if l.bias is not None else torch.zeros_like(l.scale) for l in layers])
-    fused = TernaryLinearInference(k, sum(l.out_features for l in layers), wp, scale, bias)
+    n = sum(l.out_features for l in layers)
+    if share and all(l.out_features % 16 == 0 for l in layers):
+        parts = [l._derived()[0] for l in layers]               # each member's tiled buffer (built now if need be)
+        tiled = torch.cat(parts)
+        fused = TernaryLinearInference(k, n, torch.empty(0, dtype=torch.uint8, device=scale.device), scale, bias)
+        fused.compact(tiled)
+        offset = 0
+        for l, part in zip(layers, parts):
+            view = tiled[offset:offset + part.numel()]
+            if l._compact:
+                l._tiled, l._derived_key = view, None
+            else:
+                l.compact(view)
+            offset += part.numel()
+    else:
+        wp = torch.cat([l.public_packed() for l in layers], dim=1).contiguous()
+        fused = TernaryLinearInference(k, n, wp, scale, bias)
     fused.verify_buffers = False          # private copies: nobody else can write them
     return fused
 
@@ -129,8 +150,9 @@ class _FusedColumns:
     """Runs packed sibling layers as one (``fuse_inference_columns``), rebuilt when a member's buffers change.
     Not a submodule: the members keep their names and buffers in the state dict."""
 
-    def __init__(self, *layers) -> None:
+    def __init__(self, *layers, share: bool = False) -> None:
         self.layers = layers
+        self.share = share                    # one device copy of the weights for the fused layer and its members
         self._key = None
         self._fused: Optional[TernaryLinearInference] = None
 
@@ -138,19 +160,23 @@ class _FusedColumns:
     def usable(self) -> bool:
         return all(isinstance(l, TernaryLinearInference) for l in self.layers)
 
-    def __call__(self, x: Tensor):
+    def _members_key(self):
         from ..nn.ternary_linear_cuda import capturing, content_fingerprint
 
         key = tuple((l.weight_packed.data_ptr(), l.weight_packed._version, l.scale.data_ptr(), l.scale._version)
                     for l in self.layers)
         if all(l.verify_buffers for l in self.layers) and not capturing():
             # writes through .data leave addresses and versions alone: compare sampled contents too
-            key += content_fingerprint(*[t for l in self.layers for t in (l.weight_packed, l.scale)])
-        elif self._key is not None:
-            key += self._key[len(key):]
-        if key != self._key:
-            self._fused = fuse_inference_columns(self.layers)
-            self._key = key
+            watched = [t for l in self.layers for t in ((l.scale,) if l._compact else (l.weight_packed, l.scale))]
+            return key + content_fingerprint(*watched)
+        if self._key is not None:
+            return key + self._key[len(key):]
+        return key
+
+    def __call__(self, x: Tensor):
+        if self._members_key() != self._key:
+            self._fused = fuse_inference_columns(self.layers, share=self.share)
+            self._key = self._members_key()                   # after fusing: sharing replaces the members' buffers
         return torch.split(self._fused(x), [l.out_features for l in self.layers], dim=-1)
 
 
@@ -171,7 +197,7 @@ class Attention(nn.Module):
         b, t, _ = x.shape
         hd, nh, nkv = cfg.head_dim, cfg.n_heads, cfg.n_kv_heads
         if self._fused is None or self._fused.layers != (self.q_proj, self.kv_proj):
-            self._fused = _FusedColumns(self.q_proj, self.kv_proj)
+            self._fused = _FusedColumns(self.q_proj, self.kv_proj, share=cfg.one_weight_copy)
         if self._fused.usable:                           # packed layers: one launch for both projections
             q, kv = self._fused(x)
         else:
@@ -229,11 +255,12 @@ class SwiGLU(nn.Module):
         self.w_gate = mk(cfg.dim, cfg.ffn_dim)
         self.w_up = mk(cfg.dim, cfg.ffn_dim)
         self.w_down = mk(cfg.ffn_dim, cfg.dim)
+        self.cfg = cfg
         self._fused: Optional[_FusedColumns] = None
 
     def forward(self, x: Tensor) -> Tensor:
         if self._fused is None or self._fused.layers != (self.w_gate, self.w_up):
-            self._fused = _FusedColumns(self.w_gate, self.w_up)
+            self._fused = _FusedColumns(self.w_gate, self.w_up, share=self.cfg.one_weight_copy)
         if self._fused.usable:                           # packed layers: one launch for gate and up
             gate, up = self._fused(x)
         else:
@@ -321,6 +348,12 @@ class TernaryDecoder(nn.Module):
         from .convert import convert_linear_layers
 
         convert_linear_layers(self, skip_names=["head"], inplace=True)
+        if self.cfg.one_weight_copy:
+            # proj and w_down run on their own: drop their public buffers now; the fused pairs (q/kv, gate/up) share
+            # one tiled buffer with their members the first time they run
+            for block in self.blocks:
+                block.attn.proj.compact()
+                block.mlp.w_down.compact()
         return self
 
 

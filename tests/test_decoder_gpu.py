@@ -102,7 +102,7 @@ def test_every_projection_is_the_oracles_integer_chain(oracle):
     seen_rows = set()
     for name, mod, x, y in calls:
         k, n = mod.in_features, mod.out_features
-        codes = oracle.unpack_transposed(mod.weight_packed.cpu().numpy(), k)
+        codes = oracle.unpack_transposed(mod.public_packed().cpu().numpy(), k)
         x2 = x.reshape(-1, k).float().cpu().numpy()
         q, sx = oracle.act_quant(x2)
         y_ref = oracle.epilogue(oracle.gemm_i32(q, codes), sx, mod.scale.float().cpu().numpy(), None)
@@ -165,3 +165,55 @@ def test_graph_replayed_greedy_loop_equals_the_eager_steps():
     loop.run(steps)
     torch.cuda.synchronize()
     assert torch.equal(loop.history[:, 6:6 + steps], want)
+
+
+def test_inference_form_keeps_one_copy_of_the_weights_and_checkpoints_do_not_change(tmp_path):
+    """to_inference() with one_weight_copy (the default): after the first forward every projection holds only the
+    tiled copy (the fused pairs share one buffer with their members), so device bytes per projection are
+    ceil(K/4) * N; the state dict still carries the public `weight_packed` buffers, byte for byte what a model
+    without the option holds; loading it into a fresh model reproduces the logits."""
+    from bittorch_b200.nn import TernaryLinearInference
+    from bittorch_b200.utils.decoder import DecoderConfig, TernaryDecoder
+
+    torch.manual_seed(5)
+    cfg = dict(vocab_size=VOCAB, dim=DIM, n_layers=2, n_heads=HEADS, ffn_dim=FFN, max_seq_len=32)
+    masters = TernaryDecoder(DecoderConfig(backend="python", **cfg)).cuda().eval()
+    two = TernaryDecoder(DecoderConfig(backend="cuda", one_weight_copy=False, **cfg)).cuda().eval()
+    one = TernaryDecoder(DecoderConfig(backend="cuda", **cfg)).cuda().eval()
+    for m in (two, one):
+        m.load_state_dict(masters.state_dict())
+        m.to_inference()
+    tokens = torch.randint(0, VOCAB, (3, 7), generator=torch.Generator().manual_seed(6)).cuda()
+    with torch.no_grad():
+        want = two(tokens)
+        got = one(tokens)
+        got_again = one(tokens)
+    assert torch.equal(got, want) and torch.equal(got_again, want)
+
+    weight_bytes = 0
+    storages = set()
+    for name, mod in one.named_modules():
+        if isinstance(mod, TernaryLinearInference):
+            assert mod._compact and mod.weight_packed.numel() == 0, name
+            assert mod._tiled.numel() == mod.packed_size_bytes            # dims are multiples of the tile: no padding
+            storages.add(mod._tiled.untyped_storage().data_ptr())
+            weight_bytes += mod._tiled.numel()
+    per_block = (DIM * DIM + DIM * 2 * DIM + DIM * DIM + 3 * DIM * FFN) // 4
+    assert weight_bytes == 2 * per_block
+    assert len(storages) == 2 * 4                                          # per block: fused q/kv, proj, fused gate/up, down
+    for blk in one.blocks:                                                 # the fused layers own what the members view
+        assert blk.attn._fused._fused._tiled.untyped_storage().data_ptr() == blk.attn.q_proj._tiled.untyped_storage().data_ptr()
+        assert blk.mlp._fused._fused._tiled.untyped_storage().data_ptr() == blk.mlp.w_up._tiled.untyped_storage().data_ptr()
+
+    sd_one, sd_two = one.state_dict(), two.state_dict()
+    assert set(sd_one) == set(sd_two)
+    for key in sd_two:
+        assert torch.equal(sd_one[key], sd_two[key]), key                  # wire format unchanged, byte for byte
+    path = str(tmp_path / "decoder.pt")
+    torch.save(sd_one, path)
+    fresh = TernaryDecoder(DecoderConfig(backend="cuda", **cfg)).cuda().eval()
+    fresh.load_state_dict(masters.state_dict())
+    fresh.to_inference()
+    fresh.load_state_dict(torch.load(path))
+    with torch.no_grad():
+        assert torch.equal(fresh(tokens), want)
