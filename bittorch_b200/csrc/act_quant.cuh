@@ -96,7 +96,7 @@ static int launch_act_quant(const void* X, int64_t M, int64_t K, int64_t ldx, in
                             cudaStream_t st) {
     const bool vec_in = (K % 4 == 0) && (ldx % 4 == 0) && aligned(X, 4 * sizeof(T));
     const bool vec_out = (K % 4 == 0) && aligned(Xq, 4);
-    act_quant_kernel<T><<<static_cast<unsigned>(M), AQ_THREADS, 0, st>>>(static_cast<const T*>(X), K, ldx, Xq, sx,
+    BT_LAUNCH(act_quant_kernel<T>, static_cast<unsigned>(M), AQ_THREADS, 0, st, static_cast<const T*>(X), K, ldx, Xq, sx,
                                                                          xsum, vec_in, vec_out);
     BT_LAUNCH_OK("act_quant_kernel");
     return BT_OK;

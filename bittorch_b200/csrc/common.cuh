@@ -36,6 +36,7 @@ void set_error(const char* fmt, ...);   // stores a thread-local message (lib.cu
         }                                     \
     } while (0)
 
+#ifndef BT_SIMT_HOST
 #define BT_CUDA_OK(expr)                                                              \
     do {                                                                              \
         cudaError_t e__ = (expr);                                                     \
@@ -44,6 +45,12 @@ void set_error(const char* fmt, ...);   // stores a thread-local message (lib.cu
             return BT_ERR_CUDA;                                                       \
         }                                                                             \
     } while (0)
+
+// Kernel launch with the triple-chevron syntax.  (A host build that runs the kernels as threads on the CPU, for tests,
+// defines BT_SIMT_HOST and supplies its own BT_LAUNCH, BT_LAUNCH_OK and the primitives marked below.)
+#define BT_LAUNCH(kernel, grid, block, smem, stream, ...) kernel<<<(grid), (block), (smem), (stream)>>>(__VA_ARGS__)
+// The CTA's dynamic shared memory as a byte array called `name`.
+#define BT_DYNAMIC_SMEM(name, alignment) extern __shared__ __align__(alignment) uint8_t name[]
 
 // Checks the launch that was just enqueued.
 #define BT_LAUNCH_OK(name)                                                            \
@@ -54,6 +61,15 @@ void set_error(const char* fmt, ...);   // stores a thread-local message (lib.cu
             return BT_ERR_CUDA;                                                       \
         }                                                                             \
     } while (0)
+#else
+#define BT_LAUNCH_OK(name)                                                            \
+    do {                                                                              \
+        if (::simt::error_count().load() != 0) {                                      \
+            ::bt::set_error("%s: %s", name, ::simt::error_text());                    \
+            return BT_ERR_CUDA;                                                       \
+        }                                                                             \
+    } while (0)
+#endif
 
 inline bool valid_dtype(int d) { return d == BT_F32 || d == BT_F16 || d == BT_BF16; }
 inline size_t dtype_size(int d) { return d == BT_F32 ? 4 : 2; }
@@ -72,6 +88,10 @@ int tuning(int knob);
 template <typename Kern>
 inline int ensure_dynamic_smem(Kern kern, size_t smem, std::atomic<size_t>* granted) {
     if (smem <= 48 * 1024) return BT_OK;
+#ifdef BT_SIMT_HOST
+    (void)kern; (void)granted;
+    return BT_OK;
+#else
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= BT_MAX_DEVICES) dev = -1;
     if (dev >= 0 && granted[dev].load(std::memory_order_acquire) >= smem) return BT_OK;
@@ -81,6 +101,7 @@ inline int ensure_dynamic_smem(Kern kern, size_t smem, std::atomic<size_t>* gran
         while (seen < smem && !granted[dev].compare_exchange_weak(seen, smem, std::memory_order_release)) {}
     }
     return BT_OK;
+#endif
 }
 
 // Sticky per-device status word written by kernels whose bounded waits ran out.
@@ -177,6 +198,7 @@ __device__ __forceinline__ void store_out_dt(void* Y, int dt, int64_t idx, float
     else store_out<__nv_bfloat16>(Y, idx, v);
 }
 
+#ifndef BT_SIMT_HOST
 // ---- PTX wrappers (sm_90+/sm_100a features) ---------------------------------------
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -263,5 +285,12 @@ __device__ __forceinline__ int ld_dsmem_s32(const void* local_smem_ptr, uint32_t
     asm volatile("ld.shared::cluster.s32 %0, [%1];" : "=r"(v) : "r"(remote) : "memory");
     return v;
 }
+
+// Named barrier ID over the `nthreads` threads that call it (whole warps).
+template <int ID>
+__device__ __forceinline__ void named_barrier_sync(int nthreads) {
+    asm volatile("bar.sync %0, %1;" ::"n"(ID), "r"(nthreads) : "memory");
+}
+#endif   // BT_SIMT_HOST
 
 }  // namespace bt

@@ -67,6 +67,7 @@ struct GemvTiledParams {
     int x_dtype, y_dtype;
     int x_vec;             // activation rows can be read with vector loads
     int serialized;        // host only: launch without programmatic dependent launch (weights were just written)
+    int planes;            // host only: floating-point activations as four digit planes (M = activation rows, <= 2)
     const uint32_t* amax_in;   // FUSED, optional: [M][AMAX_SLOTS] bit patterns whose maximum is the row's max |x|
     uint32_t* amax_out;        // optional: [M][AMAX_SLOTS], receives max |y as stored| over columns < amax_cols
     int amax_cols;
@@ -88,10 +89,17 @@ __device__ __forceinline__ float rounded_as_stored(float y, int dtype) {
 
 // Two CTAs per SM (<= 56 registers) for the small row counts, so that the next layer's CTAs
 // can move in and prefetch their weights while this layer finishes.
-template <int MR, bool FUSED>   // MR = activation rows padded to a power of two: 1, 2, 4 or 8
+// MODE: how the int8 rows in shared memory come about
+constexpr int GT_ROWS_INT8 = 0;    // the caller's int8 activations + scales (bt_gemv_tiled_i8)
+constexpr int GT_ROWS_FUSED = 1;   // per-token int8 quantizer inside the kernel (bt_gemv_tiled, bt_gemv_tiled_chained)
+constexpr int GT_ROWS_PLANES = 2;  // floating-point activations as four byte planes of a 32-bit fixed-point row
+                                   // (bt_gemv_tiled_float): MR / 4 activation rows
+
+template <int MR, int MODE>   // MR = int8 rows padded to a power of two: 1, 2, 4 or 8
 __global__ void __launch_bounds__(GT_THREADS, (MR <= 2) ? 2 : 1)
 gemv_tiled_kernel(const GemvTiledParams p) {
-    extern __shared__ __align__(128) uint8_t smem[];
+    constexpr bool FUSED = MODE == GT_ROWS_FUSED;
+    BT_DYNAMIC_SMEM(smem, 128);
     const int k_pad = p.KT * TILE_K;
     const int xstride = k_pad + GT_X_PAD;
     uint8_t* s_ring = smem;
@@ -107,6 +115,7 @@ gemv_tiled_kernel(const GemvTiledParams p) {
     uint64_t* s_empty = s_full + p.stages;
     __shared__ int s_abort;
     __shared__ uint32_t s_amax[GT_MAX_ROWS];               // this CTA's max |y| per row (bit patterns), amax_out only
+    __shared__ int s_bad[GT_MAX_ROWS / 4];                 // planes mode: the activation row holds an infinity or a NaN
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int stages = p.stages;
@@ -127,6 +136,7 @@ gemv_tiled_kernel(const GemvTiledParams p) {
         mbar_fence_init();
     }
     if (tid < GT_MAX_ROWS) s_amax[tid] = 0u;
+    if (tid < GT_MAX_ROWS / 4) s_bad[tid] = 0;
     for (int i = tid; i < GT_CONSUMER_WARPS * p.nbl_max * TILE_N * MR + MR + 2 * GT_CONSUMER_WARPS * MR; i += GT_THREADS)
         s_part[i] = 0;                                  // s_part, s_rowsum, s_wsum, s_wmax (0.0f)
     for (int c = tid; c < nbl * TILE_N; c += GT_THREADS) {   // epilogue constants: never written by a preceding kernel
@@ -159,7 +169,117 @@ gemv_tiled_kernel(const GemvTiledParams p) {
     } else {
         // ---- consumers --------------------------------------------------------------------------
         pdl_wait();   // activations come from the preceding kernel
-        if (FUSED) {
+        if constexpr (MODE == GT_ROWS_PLANES) {
+            // Floating-point activations, exact: with 2^e the smallest power of two above the row's max |x|,
+            //     v[k] = rint(x[k] * 2^(30-e))          (|v| < 2^30; scaling by a power of two is exact)
+            //     v    = b3 2^24 + b2 2^16 + b1 2^8 + b0  with balanced digits b in [-128, 127]
+            // and digit plane p of row m becomes int8 row 4m+p of the integer pipeline.  The epilogue recombines the
+            // four exact int32 accumulators in 64-bit arithmetic, so the output is the correctly rounded EXACT dot
+            // product of the row as represented (elements within 2^6 of the row maximum are represented exactly,
+            // the rest to 2^-30 of it) - tighter than any order of fp32 additions.
+            constexpr int ROWS = MR / 4;
+            const int tpr = GT_NCONS / ROWS;               // threads per activation row: whole warps
+            const int m = tid / tpr, j = tid % tpr;
+            const int nvec = (p.K + 3) / 4;
+            const bool row_ok = m < p.M;
+            const int64_t row_off = static_cast<int64_t>(m) * p.ldx;
+            float x[4][4];
+            float mx = 0.0f;
+            int bad = 0;                                    // an infinity or a NaN in the row
+            if (row_ok) {
+                for (int v0 = j; v0 < nvec; v0 += 4 * tpr) {
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const int v = v0 + u * tpr;
+                        const int valid = (v < nvec) ? min(4, p.K - 4 * v) : 0;
+                        if (valid > 0) load_x4(p.X, p.x_dtype, row_off + 4 * v, p.x_vec, valid, x[u]);
+                        else x[u][0] = x[u][1] = x[u][2] = x[u][3] = 0.0f;
+                    }
+#pragma unroll
+                    for (int u = 0; u < 4; ++u)
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const float a = fabsf(x[u][i]);
+                            mx = fmaxf(mx, a);
+                            bad |= !(a <= 3.402823466e38f);
+                        }
+                }
+            }
+            mx = warp_max(mx);
+            bad = warp_or(bad);
+            if (lane == 0 && row_ok) {
+                s_wmax[warp * MR + m] = mx;
+                if (bad) s_bad[m] = 1;
+            }
+            named_barrier_sync<1>(GT_NCONS);
+            float amax = 0.0f;
+#pragma unroll
+            for (int w = 0; w < GT_CONSUMER_WARPS; ++w) amax = fmaxf(amax, s_wmax[w * MR + (row_ok ? m : 0)]);
+            int e = 0;
+            frexpf(amax, &e);                               // amax = f 2^e with f in [0.5, 1): amax < 2^e
+            e = max(-96, min(127, e));                      // rows of denormal size keep a normal scale factor
+            const float mult = ldexpf(1.0f, 30 - e);
+            if (row_ok && j == 0) s_sx[4 * m] = ldexpf(1.0f, e - 30);
+            // zero what the planes below will not write: padding rows and the tail past K
+            {
+                const int vecs = xstride / 16;
+                const int first_tail = p.K / 16;
+                for (int mm = 0; mm < MR; ++mm)
+                    for (int vv = (mm >= 4 * p.M ? 0 : first_tail) + tid; vv < vecs; vv += GT_NCONS)
+                        *reinterpret_cast<uint4*>(s_x + mm * xstride + vv * 16) = make_uint4(0, 0, 0, 0);
+            }
+            if (p.K % 16 != 0) named_barrier_sync<1>(GT_NCONS);
+            int qsum[4] = {0, 0, 0, 0};
+            if (row_ok) {
+                const bool single = nvec <= 4 * tpr;        // the row stayed in registers
+                for (int v0 = j; v0 < nvec; v0 += 4 * tpr) {
+                    if (!single) {
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            const int v = v0 + u * tpr;
+                            const int valid = (v < nvec) ? min(4, p.K - 4 * v) : 0;
+                            if (valid > 0) load_x4(p.X, p.x_dtype, row_off + 4 * v, p.x_vec, valid, x[u]);
+                        }
+                    }
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const int v = v0 + u * tpr;
+                        const int valid = (v < nvec) ? min(4, p.K - 4 * v) : 0;
+                        if (valid <= 0) continue;
+                        uint32_t w[4] = {0u, 0u, 0u, 0u};   // one word of four k per digit plane
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            if (i >= valid) continue;
+                            int fx = __float2int_rn(__fmul_rn(x[u][i], mult));     // NaN -> 0; the row is flagged
+                            fx = max(-(1 << 30), min(1 << 30, fx));
+#pragma unroll
+                            for (int d = 0; d < 3; ++d) {
+                                const int b = static_cast<int>(static_cast<int8_t>(fx & 0xff));   // balanced digit
+                                w[d] |= static_cast<uint32_t>(b & 0xff) << (8 * i);
+                                fx = (fx - b) >> 8;
+                            }
+                            w[3] |= static_cast<uint32_t>(fx & 0xff) << (8 * i);                  // |fx| <= 64 now
+                        }
+                        const bool counted = ((v >> 1) & 3) != 3;      // meets weight planes 0..2 (codes t+1)
+#pragma unroll
+                        for (int d = 0; d < 4; ++d) {
+                            if (counted) qsum[d] = __dp4a(static_cast<int>(w[d]), 0x01010101, qsum[d]);
+                            int8_t* dst = s_x + (4 * m + d) * xstride + 4 * v;
+                            if (valid == 4) {
+                                *reinterpret_cast<uint32_t*>(dst) = w[d];
+                            } else {
+                                for (int i = 0; i < valid; ++i) dst[i] = static_cast<int8_t>(w[d] >> (8 * i));
+                            }
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int d = 0; d < 4; ++d) {
+                const int sum = warp_sum(qsum[d]);
+                if (lane == 0 && row_ok) s_wsum[warp * MR + 4 * m + d] = sum;
+            }
+        } else if constexpr (FUSED) {
             // thread -> (row, 4-element vector): the 512 consumer threads are split evenly over
             // the next power of two >= M rows; thread j of a row takes vectors j, j+tpr, ...
             const int tpr = GT_NCONS / MR;                  // threads per row: 512 .. 64 (whole warps)
@@ -202,7 +322,7 @@ gemv_tiled_kernel(const GemvTiledParams p) {
             } else {
                 mx = warp_max(mx);                          // a warp never straddles two rows (tpr >= 64)
                 if (lane == 0 && row_ok) s_wmax[warp * MR + m] = mx;
-                asm volatile("bar.sync 1, %0;" ::"r"(GT_NCONS) : "memory");
+                named_barrier_sync<1>(GT_NCONS);
 #pragma unroll
                 for (int w = 0; w < GT_CONSUMER_WARPS; ++w) amax = fmaxf(amax, s_wmax[w * MR + (row_ok ? m : 0)]);
             }
@@ -221,7 +341,7 @@ gemv_tiled_kernel(const GemvTiledParams p) {
                     for (int vv = (mm >= p.M ? 0 : first_tail) + tid; vv < vecs; vv += GT_NCONS)
                         *reinterpret_cast<uint4*>(s_x + mm * xstride + vv * 16) = make_uint4(0, 0, 0, 0);
             }
-            if (p.K % 16 != 0) asm volatile("bar.sync 1, %0;" ::"r"(GT_NCONS) : "memory");   // tail bytes are rewritten below
+            if (p.K % 16 != 0) named_barrier_sync<1>(GT_NCONS);   // tail bytes are rewritten below
             int qsum = 0;
             if (row_ok) {
                 const bool emit = (p.xq_out != nullptr) && blockIdx.x == 0;
@@ -274,7 +394,7 @@ gemv_tiled_kernel(const GemvTiledParams p) {
                         s_x[mm * xstride + b] = (mm < p.M && b < p.K) ? p.Xq[static_cast<int64_t>(mm) * p.K + b] : int8_t(0);
             }
             if (tid < MR) s_sx[tid] = (tid < p.M) ? p.sx[tid] : 0.0f;
-            asm volatile("bar.sync 1, %0;" ::"r"(GT_NCONS) : "memory");
+            named_barrier_sync<1>(GT_NCONS);
             // row sums: warp w sums its share of every row
             for (int mm = 0; mm < MR; ++mm) {
                 int sum = 0;
@@ -285,7 +405,7 @@ gemv_tiled_kernel(const GemvTiledParams p) {
                 if (lane == 0) s_wsum[warp * MR + mm] = sum;
             }
         }
-        asm volatile("bar.sync 1, %0;" ::"r"(GT_NCONS) : "memory");      // int8 rows complete in shared memory
+        named_barrier_sync<1>(GT_NCONS);      // int8 rows complete in shared memory
         if (tid < MR) {
             int sum = 0;
 #pragma unroll
@@ -408,6 +528,29 @@ gemv_tiled_kernel(const GemvTiledParams p) {
     }
     // epilogue: one thread per (row, column) of this CTA's column blocks, columns fastest
     const int cols = nbl * TILE_N;
+    if constexpr (MODE == GT_ROWS_PLANES) {
+        // recombine the four digit planes exactly; one rounding to float, an exact power of two, then the usual
+        // scale and bias.  A row that held an infinity or a NaN gives NaN (the reference's float kernel would
+        // propagate them through its sum).
+        for (int m = 0; m < p.M; ++m)
+            for (int c = tid; c < cols; c += GT_THREADS) {
+                const int n = nb0 * TILE_N + c;
+                if (n >= p.N) continue;
+                long long total = 0;
+#pragma unroll
+                for (int d = 3; d >= 0; --d) {
+                    int acc = -s_rowsum[4 * m + d];
+#pragma unroll
+                    for (int w = 0; w < GT_CONSUMER_WARPS; ++w) acc += s_part[(w * p.nbl_max * TILE_N + c) * MR + 4 * m + d];
+                    total = total * 256 + acc;
+                }
+                float y = __fmul_rn(__fmul_rn(__ll2float_rn(total), s_sx[4 * m]), s_scale[c]);
+                if (p.bias != nullptr) y = __fadd_rn(y, s_bias[c]);
+                if (s_bad[m]) y = __int_as_float(0x7fc00000);
+                store_out_dt(p.Y, p.y_dtype, static_cast<int64_t>(m) * p.ldy + n, y);
+            }
+        return;
+    }
     const bool publish = p.amax_out != nullptr;
     for (int m = 0; m < p.M; ++m) {
         float ymax = 0.0f;
@@ -453,9 +596,15 @@ static int gemv_tiled_rows_per_launch(int64_t K) {
     return rows;
 }
 
-template <int MR, bool FUSED>
+template <int MR, int MODE>
 static int launch_gemv_tiled_kernel(const GemvTiledParams& p, int grid, size_t smem, cudaStream_t st) {
-    auto kern = gemv_tiled_kernel<MR, FUSED>;
+    auto kern = gemv_tiled_kernel<MR, MODE>;
+#ifdef BT_SIMT_HOST
+    (void)st;
+    const int rc = ::simt::launch(kern, dim3(grid), dim3(GT_THREADS), smem, p);
+    if (rc != BT_OK) set_error("gemv_tiled_kernel: %s", ::simt::error_text());
+    return rc;
+#else
     static std::atomic<size_t> granted[BT_MAX_DEVICES];
     if (const int rc = ensure_dynamic_smem(kern, smem, granted)) return rc;
     cudaLaunchConfig_t cfg = {};
@@ -473,25 +622,36 @@ static int launch_gemv_tiled_kernel(const GemvTiledParams& p, int grid, size_t s
     cfg.numAttrs = p.serialized ? 0 : 1;
     BT_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, p));
     return BT_OK;
+#endif
 }
 
-// One launch over `p.M` <= GT_MAX_ROWS rows.
+// One launch over `p.M` <= GT_MAX_ROWS rows (planes: <= 2 activation rows = 8 int8 rows).
 static int launch_gemv_tiled_rows(GemvTiledParams p, cudaStream_t st) {
     p.KT = ceil_div(p.K, TILE_K);
     p.NB = ceil_div(p.N, TILE_N);
-    const int mr = (p.M <= 1) ? 1 : (p.M <= 2) ? 2 : (p.M <= 4) ? 4 : 8;
+    const int rows8 = p.planes ? 4 * p.M : p.M;               // int8 rows held in shared memory
+    const int mr = (rows8 <= 1) ? 1 : (rows8 <= 2) ? 2 : (rows8 <= 4) ? 4 : 8;
     // one CTA per SM; more CTAs only when a CTA's partial-sum slots would outgrow their budget
     const int nbl_cap = std::max(1, GT_SLOT_BUDGET / mr);
     const int grid = std::max(std::min(p.NB, sm_count()), ceil_div(p.NB, nbl_cap));
     p.nbl_max = ceil_div(p.NB, grid);
     const int max_tiles = p.nbl_max * p.KT;
     p.stages = std::max(1, std::min(GT_MAX_STAGES, ceil_div(max_tiles, GT_STAGE_TILES)));
-    const size_t smem = gemv_tiled_smem(mr, p.KT * TILE_K, p.nbl_max, p.stages);
+    size_t smem = gemv_tiled_smem(mr, p.KT * TILE_K, p.nbl_max, p.stages);
+    while (smem > 227 * 1024 && p.stages > 1) {               // long rows: a shallower weight ring makes room
+        --p.stages;
+        smem = gemv_tiled_smem(mr, p.KT * TILE_K, p.nbl_max, p.stages);
+    }
     BT_UNSUPPORTED_IF(smem > 227 * 1024, "gemv_tiled: needs %zu bytes of shared memory (K too large)", smem);
+    if (p.planes) {
+        if (mr == 4) return launch_gemv_tiled_kernel<4, GT_ROWS_PLANES>(p, grid, smem, st);
+        return launch_gemv_tiled_kernel<8, GT_ROWS_PLANES>(p, grid, smem, st);
+    }
     const bool fused = p.X != nullptr;
 #define BT_GEMV_CASE(MRV)                                                                       \
     if (mr == MRV)                                                                              \
-        return fused ? launch_gemv_tiled_kernel<MRV, true>(p, grid, smem, st) : launch_gemv_tiled_kernel<MRV, false>(p, grid, smem, st);
+        return fused ? launch_gemv_tiled_kernel<MRV, GT_ROWS_FUSED>(p, grid, smem, st)          \
+                     : launch_gemv_tiled_kernel<MRV, GT_ROWS_INT8>(p, grid, smem, st);
     BT_GEMV_CASE(1)
     BT_GEMV_CASE(2)
     BT_GEMV_CASE(4)
@@ -502,7 +662,9 @@ static int launch_gemv_tiled_rows(GemvTiledParams p, cudaStream_t st) {
 
 // Splits M rows into launches of at most gemv_tiled_rows_per_launch(K) rows over the same weights.
 static int launch_gemv_tiled(const GemvTiledParams& p, cudaStream_t st) {
-    const int rows = gemv_tiled_rows_per_launch(p.K);
+    // planes: two activation rows (eight int8 rows) per launch where they fit next to the partial sums, else one
+    const int rows = p.planes ? ((8 * (ceil_div<int64_t>(p.K, TILE_K) * TILE_K + GT_X_PAD) <= 96 * 1024) ? 2 : 1)
+                              : gemv_tiled_rows_per_launch(p.K);
     for (int m0 = 0; m0 < p.M; m0 += rows) {
         GemvTiledParams q = p;
         q.M = std::min(rows, p.M - m0);
@@ -594,5 +756,23 @@ extern "C" int bt_gemv_tiled_chained(const void* X, int x_dtype, int64_t M, int6
     p.X = X; p.x_dtype = x_dtype; p.ldx = ldx;
     p.x_vec = (K % 4 == 0) && (ldx % 4 == 0) && aligned(X, 4 * dtype_size(x_dtype));
     p.amax_in = amax_in; p.amax_out = amax_out; p.amax_cols = static_cast<int>(amax_cols);
+    return launch_gemv_tiled(p, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int bt_gemv_tiled_float(const void* X, int x_dtype, int64_t M, int64_t K, int64_t ldx, const uint8_t* tiled,
+                                   int64_t N, const float* scale, const float* bias, void* Y, int y_dtype, int64_t ldy,
+                                   int flags, void* stream) {
+    using namespace bt;
+    BT_REQUIRE(X != nullptr, "bt_gemv_tiled_float: NULL pointer");
+    BT_REQUIRE((flags & ~BT_LAUNCH_WEIGHTS_JUST_WRITTEN) == 0, "bt_gemv_tiled_float: unknown flags %d", flags);
+    BT_REQUIRE(valid_dtype(x_dtype), "bt_gemv_tiled_float: unknown activation dtype %d", x_dtype);
+    BT_REQUIRE(ldx >= K, "bt_gemv_tiled_float: row stride %lld < K %lld", (long long)ldx, (long long)K);
+    int rc = check_gemv_tiled_args("bt_gemv_tiled_float", M, K, tiled, N, scale, Y, y_dtype, ldy);
+    if (rc != BT_OK) return rc;
+    // digits reach -128: half the K of the int8 kernels keeps every 32-bit partial sum exact
+    BT_UNSUPPORTED_IF(K > BT_MAX_K / 2, "bt_gemv_tiled_float: K=%lld exceeds %d", (long long)K, BT_MAX_K / 2);
+    GemvTiledParams p = base_tiled_params(M, K, tiled, N, scale, bias, Y, y_dtype, ldy, nullptr, flags);
+    p.X = X; p.x_dtype = x_dtype; p.ldx = ldx; p.planes = 1;
+    p.x_vec = (K % 4 == 0) && (ldx % 4 == 0) && aligned(X, 4 * dtype_size(x_dtype));
     return launch_gemv_tiled(p, static_cast<cudaStream_t>(stream));
 }

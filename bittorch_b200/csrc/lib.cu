@@ -110,7 +110,7 @@ extern "C" int bt_set_tuning(int knob, int value) {
 
 extern "C" int bt_selftest_wait_timeout(void* stream) {
     using namespace bt;
-    wait_timeout_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(2048);
+    BT_LAUNCH(wait_timeout_selftest_kernel, 1, 32, 0, static_cast<cudaStream_t>(stream), 2048);
     BT_LAUNCH_OK("wait_timeout_selftest_kernel");
     return BT_OK;
 }

@@ -103,13 +103,13 @@ static int launch_linear_float(const char* who, const void* X, int x_dtype, int6
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int m = static_cast<int>(M), k = static_cast<int>(K), n = static_cast<int>(N);
     if (x_dtype == BT_F32)
-        linear_float_kernel<float, PACKED><<<grid, LF_THREADS, 0, st>>>(static_cast<const float*>(X), m, k, W, n, scale, bias, static_cast<float*>(Y));
+        BT_LAUNCH((linear_float_kernel<float, PACKED>), grid, LF_THREADS, 0, st, static_cast<const float*>(X), m, k, W, n, scale, bias, static_cast<float*>(Y));
     else if (x_dtype == BT_F64)   // float64 containers, float32 arithmetic (csrc/kernels/ternary_gemm.cu:56-61)
-        linear_float_kernel<double, PACKED><<<grid, LF_THREADS, 0, st>>>(static_cast<const double*>(X), m, k, W, n, scale, bias, static_cast<double*>(Y));
+        BT_LAUNCH((linear_float_kernel<double, PACKED>), grid, LF_THREADS, 0, st, static_cast<const double*>(X), m, k, W, n, scale, bias, static_cast<double*>(Y));
     else if (x_dtype == BT_F16)
-        linear_float_kernel<__half, PACKED><<<grid, LF_THREADS, 0, st>>>(static_cast<const __half*>(X), m, k, W, n, scale, bias, static_cast<__half*>(Y));
+        BT_LAUNCH((linear_float_kernel<__half, PACKED>), grid, LF_THREADS, 0, st, static_cast<const __half*>(X), m, k, W, n, scale, bias, static_cast<__half*>(Y));
     else
-        linear_float_kernel<__nv_bfloat16, PACKED><<<grid, LF_THREADS, 0, st>>>(static_cast<const __nv_bfloat16*>(X), m, k, W, n, scale, bias, static_cast<__nv_bfloat16*>(Y));
+        BT_LAUNCH((linear_float_kernel<__nv_bfloat16, PACKED>), grid, LF_THREADS, 0, st, static_cast<const __nv_bfloat16*>(X), m, k, W, n, scale, bias, static_cast<__nv_bfloat16*>(Y));
     BT_LAUNCH_OK("linear_float_kernel");
     return BT_OK;
 }

@@ -214,7 +214,7 @@ static int launch_quantize_pack(const void* W, int64_t N, int64_t K, int64_t ldw
                                 float* scale, int8_t* codes, void* tern, cudaStream_t st) {
     const bool vec = (K % 4 == 0) && (ldw % 4 == 0) && aligned(W, 4 * sizeof(T));
     const unsigned grid = static_cast<unsigned>(ceil_div<int64_t>(N, QP_ROWS));
-    quantize_pack_kernel<T><<<grid, QP_THREADS, 0, st>>>(static_cast<const T*>(W), N, K, ldw, tf, packed_T, scale,
+    BT_LAUNCH(quantize_pack_kernel<T>, grid, QP_THREADS, 0, st, static_cast<const T*>(W), N, K, ldw, tf, packed_T, scale,
                                                           codes, static_cast<T*>(tern), vec);
     BT_LAUNCH_OK("quantize_pack_kernel");
     return BT_OK;
@@ -242,7 +242,7 @@ extern "C" int bt_pack_codes(const int8_t* codes, int64_t N, int64_t K, uint8_t*
     BT_REQUIRE(codes != nullptr && packed_T != nullptr, "bt_pack_codes: NULL pointer");
     BT_REQUIRE(N > 0 && K > 0, "bt_pack_codes: empty weight");
     const unsigned grid = static_cast<unsigned>(ceil_div<int64_t>(N, QP_ROWS));
-    pack_codes_kernel<<<grid, QP_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(codes, N, K, packed_T);
+    BT_LAUNCH(pack_codes_kernel, grid, QP_THREADS, 0, static_cast<cudaStream_t>(stream), codes, N, K, packed_T);
     BT_LAUNCH_OK("pack_codes_kernel");
     return BT_OK;
 }
@@ -253,7 +253,7 @@ extern "C" int bt_unpack_codes(const uint8_t* packed_T, int64_t N, int64_t K, in
     BT_REQUIRE(N > 0 && K > 0, "bt_unpack_codes: empty weight");
     const int64_t total = N * K;
     const unsigned grid = static_cast<unsigned>(std::min<int64_t>(ceil_div<int64_t>(total, 256), sm_count() * 16));
-    unpack_codes_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(packed_T, N, K, codes);
+    BT_LAUNCH(unpack_codes_kernel, grid, 256, 0, static_cast<cudaStream_t>(stream), packed_T, N, K, codes);
     BT_LAUNCH_OK("unpack_codes_kernel");
     return BT_OK;
 }
@@ -264,7 +264,7 @@ extern "C" int bt_pack_codes_rows(const int8_t* codes, int64_t N, int64_t K, uin
     BT_REQUIRE(N > 0 && K > 0, "bt_pack_codes_rows: empty weight");
     const int64_t total = N * ceil_div<int64_t>(K, 4);
     const unsigned grid = static_cast<unsigned>(std::min<int64_t>(ceil_div<int64_t>(total, 256), sm_count() * 16));
-    pack_codes_rows_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(codes, N, K, packed);
+    BT_LAUNCH(pack_codes_rows_kernel, grid, 256, 0, static_cast<cudaStream_t>(stream), codes, N, K, packed);
     BT_LAUNCH_OK("pack_codes_rows_kernel");
     return BT_OK;
 }
@@ -275,7 +275,7 @@ extern "C" int bt_unpack_codes_rows(const uint8_t* packed, int64_t N, int64_t K,
     BT_REQUIRE(N > 0 && K > 0, "bt_unpack_codes_rows: empty weight");
     const int64_t total = N * K;
     const unsigned grid = static_cast<unsigned>(std::min<int64_t>(ceil_div<int64_t>(total, 256), sm_count() * 16));
-    unpack_codes_rows_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(packed, N, K, codes);
+    BT_LAUNCH(unpack_codes_rows_kernel, grid, 256, 0, static_cast<cudaStream_t>(stream), packed, N, K, codes);
     BT_LAUNCH_OK("unpack_codes_rows_kernel");
     return BT_OK;
 }

@@ -96,7 +96,7 @@ extern "C" int bt_retile_packed(const uint8_t* packed_T, int64_t K, int64_t N, u
     BT_UNSUPPORTED_IF(K > BT_MAX_K || N > (int64_t{1} << 30), "bt_retile_packed: shape too large");
     const int KT = static_cast<int>(ceil_div<int64_t>(K, TILE_K)), NB = static_cast<int>(ceil_div<int64_t>(N, TILE_N));
     BT_UNSUPPORTED_IF(NB > 65535, "bt_retile_packed: N too large for one launch");
-    retile_kernel<<<dim3(KT, NB), 128, 0, static_cast<cudaStream_t>(stream)>>>(packed_T, static_cast<int>(K),
+    BT_LAUNCH(retile_kernel, dim3(KT, NB), 128, 0, static_cast<cudaStream_t>(stream), packed_T, static_cast<int>(K),
                                                                                 static_cast<int>(N), KT, tiled);
     BT_LAUNCH_OK("retile_kernel");
     return BT_OK;
@@ -110,7 +110,7 @@ extern "C" int bt_untile_packed(const uint8_t* tiled, int64_t K, int64_t N, uint
     const int KT = static_cast<int>(ceil_div<int64_t>(K, TILE_K));
     const int64_t total = ceil_div<int64_t>(K, 4) * N;
     const unsigned grid = static_cast<unsigned>(std::min<int64_t>(ceil_div<int64_t>(total, 256), sm_count() * 16));
-    untile_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(tiled, static_cast<int>(K), static_cast<int>(N), KT,
+    BT_LAUNCH(untile_kernel, grid, 256, 0, static_cast<cudaStream_t>(stream), tiled, static_cast<int>(K), static_cast<int>(N), KT,
                                                                        packed_T);
     BT_LAUNCH_OK("untile_kernel");
     return BT_OK;

@@ -237,6 +237,25 @@ int bt_gemv_tiled_chained(const void* X, int x_dtype, int64_t M, int64_t K, int6
                           uint32_t* amax_out, int64_t amax_cols, int flags, void* stream);
 
 /*
+ * Decode-size packed ternary linear with FLOATING-POINT activations (no activation
+ * quantization): Y[m,n] = (sum_k X[m,k] * T[n,k]) * scale[n] + bias[n], the arithmetic of
+ * the reference's packed float kernel (csrc/kernels/ternary_gemm_production.cu:53-142,
+ * decode (c==1)-(c==2) at :37-39) on the tiled layout at the decode kernel's streaming rate.
+ * The sum is computed EXACTLY: each activation row is rescaled by a power of two into 32-bit
+ * fixed point (elements within 2^6 of the row's largest magnitude exactly, the rest to 2^-30
+ * of it), split into four signed-byte digit planes that go through the integer pipeline as
+ * four int8 rows, and recombined in 64-bit arithmetic; one rounding to float follows, then
+ * scale and bias.  The result is therefore independent of summation order and at least as
+ * close to the real-number result as the reference's fp32 accumulation (whose own tests allow
+ * 1e-4, tests/test_packed_kernel.py:50).  A row containing an infinity or a NaN yields NaN.
+ * X [M,K] row stride ldx, dtype x_dtype, M <= BT_GEMV_MAX_M (two rows per launch), K <=
+ * BT_MAX_K / 2; other arguments and `flags` as bt_gemv_tiled.
+ */
+int bt_gemv_tiled_float(const void* X, int x_dtype, int64_t M, int64_t K, int64_t ldx,
+                        const uint8_t* tiled, int64_t N, const float* scale, const float* bias,
+                        void* Y, int y_dtype, int64_t ldy, int flags, void* stream);
+
+/*
  * Prefill-size packed ternary linear on int8 activations (any M >= 1), same
  * arithmetic as above, contraction on the 5th-generation tensor cores
  * (tcgen05.mma kind::i8, accumulators in tensor memory).  Reads the tiled layout.
