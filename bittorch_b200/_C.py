@@ -55,6 +55,7 @@ _SIGNATURES = {
     "bt_gemv_tiled_i8": ([_p, _p, _i64, _i64, _p, _i64, _p, _p, _p, _int, _i64, _p, _int, _p], _int),
     "bt_gemv_tiled": ([_p, _int, _i64, _i64, _i64, _p, _i64, _p, _p, _p, _int, _i64, _p, _p, _p, _int, _p], _int),
     "bt_gemv_tiled_chained": ([_p, _int, _i64, _i64, _i64, _p, _i64, _p, _p, _p, _int, _i64, _p, _p, _i64, _int, _p], _int),
+    "bt_gemv_tiled_float": ([_p, _int, _i64, _i64, _i64, _p, _i64, _p, _p, _p, _int, _i64, _int, _p], _int),
     "bt_gemm_tiled_i8": ([_p, _p, _p, _i64, _i64, _p, _i64, _p, _p, _p, _int, _i64, _p, _p], _int),
     "bt_linear_unpacked": ([_p, _int, _i64, _i64, _p, _i64, _p, _p, _p, _p], _int),
     "bt_linear_packed_float": ([_p, _int, _i64, _i64, _p, _i64, _p, _p, _p, _p], _int),
@@ -320,6 +321,30 @@ def gemv_tiled(x2d: Tensor, tiled: Tensor, in_features: int, out_features: int, 
                                   _ptr(scale), _ptr(bias), _ptr(y), _DT[y.dtype], y.stride(0), _ptr(xq), _ptr(sx), _ptr(acc),
                                   LAUNCH_WEIGHTS_JUST_WRITTEN if fresh_weights else LAUNCH_DEFAULT, _stream(x2d)))
     return (y, xq, sx, acc) if want_debug else y
+
+
+FLOAT_GEMV_MAX_K = 65536     # bt_gemv_tiled_float: digits reach -128, half the K of the int8 kernels
+
+
+def gemv_tiled_float(x2d: Tensor, tiled: Tensor, in_features: int, out_features: int, scale: Tensor,
+                     bias: Optional[Tensor] = None, out: Optional[Tensor] = None, fresh_weights: bool = False) -> Tensor:
+    """Decode-size linear with floating-point activations (no activation quantization) on the tiled layout: the
+    reference's float semantics computed exactly (four digit planes of a 32-bit fixed-point row through the integer
+    pipeline).  M <= GEMV_MAX_M, K <= FLOAT_GEMV_MAX_K."""
+    if x2d.stride(1) != 1:
+        x2d = x2d.contiguous()
+    m = x2d.shape[0]
+    y = torch.empty((m, out_features), dtype=x2d.dtype, device=x2d.device) if out is None else out
+    with torch.cuda.device(x2d.device):
+        _check(_lib.bt_gemv_tiled_float(_ptr(x2d), _dtype_code(x2d, "X"), m, in_features, x2d.stride(0), _ptr(tiled),
+                                        out_features, _ptr(scale), _ptr(bias), _ptr(y), _DT[y.dtype], y.stride(0),
+                                        LAUNCH_WEIGHTS_JUST_WRITTEN if fresh_weights else LAUNCH_DEFAULT, _stream(x2d)))
+    return y
+
+
+def float_linear_tiled_ok(m: int, in_features: int, dtype: torch.dtype) -> bool:
+    """Float mode runs the tiled decode kernel for small batches; everything else the general float kernel."""
+    return m <= DECODE_MAX_M and in_features <= FLOAT_GEMV_MAX_K and dtype in _DT
 
 
 def new_amax_buffer(layers: int, rows: int, device) -> Tensor:

@@ -133,10 +133,13 @@ class TernaryLinearCUDAFunction(torch.autograd.Function):
         packed_T, tiled, scale, fresh = _quantized(weight.detach(), threshold_factor, cache)
         b32 = None if bias is None else bias.detach().to(torch.float32).contiguous()
         x2d = x.detach().contiguous().reshape(-1, k)
+        fresh = fresh or (b32 is not None and b32.data_ptr() != bias.data_ptr())     # a float32 copy made just now
         if C.activation_mode() == "float" or x2d.dtype == torch.float64:      # float64 has no int8 path
-            y2d = C.ternary_linear_packed_forward(x2d, packed_T, scale, b32, k)
+            if C.float_linear_tiled_ok(x2d.shape[0], k, x2d.dtype):
+                y2d = C.gemv_tiled_float(x2d, tiled, k, n, scale, b32, fresh_weights=fresh)
+            else:
+                y2d = C.ternary_linear_packed_forward(x2d, packed_T, scale, b32, k)
         else:
-            fresh = fresh or (b32 is not None and b32.data_ptr() != bias.data_ptr())     # a float32 copy made just now
             y2d = C.int8_linear_tiled(x2d, tiled, k, n, scale, b32, fresh_weights=fresh)
         ctx.save_for_backward(x, packed_T, scale)
         ctx.has_bias = bias is not None

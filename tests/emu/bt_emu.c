@@ -397,6 +397,57 @@ int bt_gemv_tiled_chained(const void* X, int x_dtype, int64_t M, int64_t K, int6
     return rc;
 }
 
+/* bt_gemv_tiled_float by its definition: 32-bit fixed point from the row maximum's power of two, exact contraction. */
+int bt_gemv_tiled_float(const void* X, int x_dtype, int64_t M, int64_t K, int64_t ldx, const uint8_t* tiled, int64_t N,
+                        const float* scale, const float* bias, void* Y, int y_dtype, int64_t ldy, int flags, void* stream) {
+    (void)stream;
+    REQUIRE(X != NULL, "bt_gemv_tiled_float: NULL pointer");
+    REQUIRE((flags & ~BT_LAUNCH_WEIGHTS_JUST_WRITTEN) == 0, "bt_gemv_tiled_float: unknown flags %d", flags);
+    REQUIRE(valid_dtype(x_dtype), "bt_gemv_tiled_float: unknown activation dtype %d", x_dtype);
+    REQUIRE(ldx >= K, "bt_gemv_tiled_float: row stride < K");
+    int rc = check_linear("bt_gemv_tiled_float", M, K, tiled, N, scale, Y, y_dtype, ldy);
+    if (rc) return rc;
+    if (M > BT_GEMV_MAX_M) return fail(BT_ERR_UNSUPPORTED, "bt_gemv_tiled_float: M=%lld exceeds %d", (long long)M, BT_GEMV_MAX_M);
+    if (K > BT_MAX_K / 2) return fail(BT_ERR_UNSUPPORTED, "bt_gemv_tiled_float: K=%lld exceeds %d", (long long)K, BT_MAX_K / 2);
+    float* x = widen(X, x_dtype, M, K, ldx);
+    int8_t* codes = codes_from_tiled(tiled, K, N);
+    int64_t* v = (int64_t*)malloc(sizeof(int64_t) * (size_t)K);
+    for (int64_t m = 0; m < M; ++m) {
+        const float* row = x + m * K;
+        float amax = 0.0f;
+        int bad = 0;
+        for (int64_t k = 0; k < K; ++k) {
+            float a = fabsf(row[k]);
+            amax = fmaxf(amax, a);
+            if (!(a <= 3.402823466e38f)) bad = 1;
+        }
+        int e = 0;
+        frexpf(amax, &e);
+        if (e < -96) e = -96;
+        if (e > 127) e = 127;
+        float mult = ldexpf(1.0f, 30 - e), back = ldexpf(1.0f, e - 30);
+        for (int64_t k = 0; k < K; ++k) {
+            float p = row[k] * mult;
+            int64_t q = (p != p) ? 0 : (int64_t)nearbyintf(p);
+            if (q > (1 << 30)) q = 1 << 30;
+            if (q < -(1 << 30)) q = -(1 << 30);
+            v[k] = q;
+        }
+        for (int64_t n = 0; n < N; ++n) {
+            int64_t total = 0;
+            for (int64_t k = 0; k < K; ++k) total += v[k] * codes[n * K + k];
+            float y = ((float)total * back) * scale[n];
+            if (bias) y = y + bias[n];
+            if (bad) y = NAN;
+            store_elem(Y, y_dtype, m * ldy + n, y);
+        }
+    }
+    free(v);
+    free(codes);
+    free(x);
+    return BT_OK;
+}
+
 int bt_gemm_tiled_i8(const int8_t* Xq, const float* sx, const int32_t* xsum, int64_t M, int64_t K, const uint8_t* tiled,
                      int64_t N, const float* scale, const float* bias, void* Y, int y_dtype, int64_t ldy,
                      int32_t* acc_out, void* stream) {

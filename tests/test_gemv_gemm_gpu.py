@@ -386,3 +386,62 @@ def test_chained_layers_with_published_row_maxima_give_the_same_bits(oracle, m, 
         got = amax[i].max(dim=1).values.view(torch.float32) if amax[i].dtype == torch.int32 else None
         assert torch.equal(got.cpu(), want.cpu())
     assert _C.device_status() == 0
+
+
+def _planes_definition(x32, codes, scale, bias):
+    """bt_gemv_tiled_float's definition in numpy: fixed point from the row maximum's power of two, exact integer
+    contraction, one rounding to float32, exact power of two, scale, bias (unfused float32 operations)."""
+    y = np.empty((x32.shape[0], codes.shape[0]), np.float32)
+    for r in range(x32.shape[0]):
+        row = x32[r]
+        e = max(-96, min(127, int(np.frexp(np.float32(np.abs(row).max()))[1])))
+        v = np.clip(np.rint(row * np.float32(2.0 ** (30 - e))).astype(np.int64), -(1 << 30), 1 << 30)
+        total = codes.astype(np.int64) @ v
+        out = (total.astype(np.float32) * np.float32(2.0 ** (e - 30))) * scale
+        y[r] = out + bias if bias is not None else out
+    return y
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("m,k,n", [(1, 4096, 4096), (1, 4096, 11008), (2, 2560, 6912), (4, 1024, 640), (3, 200, 50),
+                                   (1, 28672, 256), (16, 65, 129), (1, 1, 1), (5, 100, 300)])
+def test_float_activation_gemv_is_the_exact_contraction(oracle, m, k, n, dtype):
+    """Float mode at decode sizes (bt_gemv_tiled_float): bit-identical to its definition (the exact contraction of
+    the fixed-point rows), and within the reference's own tolerance (1e-4, tests/test_packed_kernel.py:50) of the
+    float semantics as the oracle states them (fp64 accumulation)."""
+    from bittorch_b200 import _C
+
+    g = torch.Generator().manual_seed(m * 3 + k + n)
+    codes = torch.randint(-1, 2, (n, k), generator=g, dtype=torch.int8)
+    x = (torch.randn(m, k, generator=g) * 0.7).to(dtype)
+    scale = torch.rand(n, generator=g) * 0.05 + 0.01
+    bias = torch.randn(n, generator=g)
+    tiled = _C.retile(_C.pack_codes(codes.cuda()), k)
+    torch.cuda.synchronize()
+    y = _C.gemv_tiled_float(x.cuda(), tiled, k, n, scale.cuda(), bias.cuda())
+    torch.cuda.synchronize()
+    assert _C.device_status() == 0
+    want = _planes_definition(x.float().numpy(), codes.numpy(), scale.numpy(), bias.numpy())
+    assert torch.equal(y.cpu(), torch.from_numpy(want).to(dtype))
+    y_ref = oracle.linear_float(x.float().numpy(), codes.numpy(), scale.numpy(), bias.numpy())
+    tol = 1e-4 if dtype == torch.float32 else 1e-2
+    assert np.allclose(y.float().cpu().numpy(), y_ref, rtol=tol, atol=tol)
+
+
+def test_float_mode_of_the_inference_module_streams_the_tiled_weights(oracle, monkeypatch):
+    """BITTORCH_B200_ACT=float: small batches go through bt_gemv_tiled_float, large ones through the general float
+    kernel; both within 1e-4 of the float semantics, and of each other."""
+    import bittorch_b200 as bt
+
+    monkeypatch.setenv("BITTORCH_B200_ACT", "float")
+    g = torch.Generator().manual_seed(12)
+    k, n = 520, 200
+    w = torch.randn(n, k, generator=g)
+    layer = bt.nn.create_ternary_linear_inference(k, n, w.cuda(), torch.randn(n, generator=g).cuda())
+    codes, scale = oracle.ternarize(w.numpy(), 0.05)
+    x = torch.randn(40, k, generator=g)
+    y_ref = oracle.linear_float(x.numpy(), codes, scale, layer.bias.cpu().numpy())
+    small = torch.cat([layer(x[i:i + 4].cuda()) for i in range(0, 40, 4)])      # decode kernel, 4 rows at a time
+    large = layer(x.cuda())                                                       # general kernel
+    assert np.allclose(small.cpu().numpy(), y_ref, rtol=1e-4, atol=1e-4)
+    assert np.allclose(large.cpu().numpy(), y_ref, rtol=1e-4, atol=1e-4)
