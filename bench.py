@@ -344,8 +344,9 @@ def launch_linear(layer: Layer, m: int, x: torch.Tensor, ldx: int, y: torch.Tens
 def make_chain_step(layers, m: int, x0: torch.Tensor, ranks: Ranks, gather: bool = True, published: bool = False):
     """Returns (step_fn, launches per step) for a chain of layers: the next layer reads the first K columns of the
     previous output.  `published` (one GPU, decode kernel): every layer publishes its output rows' maxima and the
-    next layer takes its quantization scale from them (bt_gemv_tiled_chained; one memset of the maxima per step).  world > 1 and `gather`: each layer's [M, N/p] shard outputs are all-gathered (NCCL) into
-    [p][M][N/p] and, for M > 1, transposed into [M, N] by one copy.  world > 1 and not `gather`: the same kernels
+    next layer takes its quantization scale from them (bt_gemv_tiled_chained; one memset of the maxima per step).
+    world > 1 and `gather`: each layer's [M, N/p] shard outputs are all-gathered (NCCL) into [p][M][N/p] and, for
+    M > 1, transposed into [M, N] by one copy.  world > 1 and not `gather`: the same kernels
     with the collective taken out (each layer reads a fixed input), which is what the gathers' cost is measured
     against.  Buffers are allocated once; step_fn only enqueues."""
     import torch.distributed as dist
@@ -373,7 +374,7 @@ def make_chain_step(layers, m: int, x0: torch.Tensor, ranks: Ranks, gather: bool
 
     def step_published():
         lib, st = _C._lib, _C._stream(x0)
-        amax.zero_()
+        amax.fill_(0)          # a fill kernel rather than a memset: the chain stays kernel -> kernel inside the graph
         x, ldx = x0, x0.stride(0)
         for i, l in enumerate(layers):
             next_k = layers[i + 1].k if i + 1 < len(layers) else l.n_local
@@ -1004,7 +1005,6 @@ def main() -> None:
     ranks = Ranks(world, rank, group, dev)
     peaks = load_peaks()
     traffic = load_traffic_ratio()
-    sampler = ClockSampler(local_rank).start()
 
     chain = ProjectionChain(dev, rank, world, seed=0, keep_packed=True)
     x0 = torch.randn(1, chain.layers[0].k, generator=torch.Generator().manual_seed(1)).to(torch.bfloat16).to(dev)
@@ -1017,13 +1017,18 @@ def main() -> None:
         published = res.get("ok") is True
         if not published:
             published_note = res.get("error", "outputs differ from the plain chain")
+    sampler = ClockSampler(local_rank).start()                 # before every warm-up of the timed chains
     quick = {}
     if published:                                              # a short run of each; the headline takes the faster
-        for name, flag in (("plain", False), ("published_row_maxima", True)):
-            r = time_chain(chain.layers, 1, x0, ranks, True, args.steps, args.warmup, 0.3, published=flag)
-            r.pop("graph").reset()
-            quick[name] = r["ms_per_step"]
-        published = quick["published_row_maxima"] <= quick["plain"]
+        try:
+            for name, flag in (("plain", False), ("published_row_maxima", True)):
+                r = time_chain(chain.layers, 1, x0, ranks, True, args.steps, args.warmup, 0.3, published=flag)
+                r.pop("graph").reset()
+                quick[name] = r["ms_per_step"]
+            published = quick["published_row_maxima"] <= quick["plain"]
+        except Exception as exc:      # noqa: BLE001  (the plain chain is the fallback, not an error of the bench)
+            published, published_note = False, f"{type(exc).__name__}: {exc}"[:300]
+            torch.cuda.synchronize()
 
     # ---- headline: the chain (with its all-gathers when sharded), >= MIN_TIMED_S of timed replays -------------
     head = time_chain(chain.layers, 1, x0, ranks, True, args.steps, args.warmup, MIN_TIMED_S,
