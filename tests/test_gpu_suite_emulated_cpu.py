@@ -13,7 +13,9 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 def test_gpu_marked_files_pass_against_the_emulated_library():
     files = ["tests/test_act_quant_gpu.py", "tests/test_quantize_pack_gpu.py", "tests/test_modules_gpu.py",
-             "tests/test_decoder_gpu.py", "tests/test_gemv_gemm_gpu.py"]
+             "tests/test_gemv_gemm_gpu.py", "tests/test_serving_decoder_gpu.py",
+             "tests/test_tensor_core_full_rows_gpu.py", "tests/test_tiled_gemv_variants_gpu.py",
+             "tests/test_weight_caches_and_new_entries_gpu.py"]
     runner = os.path.join(ROOT, "tests", "emu", "run_pytest.py")
     subprocess.run([sys.executable, "-c", "from tests.emu import runtime; runtime.build()"], check=True, cwd=ROOT)
     env = dict(os.environ, OMP_NUM_THREADS="2", MKL_NUM_THREADS="2")          # five processes share the host cores

@@ -217,106 +217,3 @@ def test_autocast_forward_backward():
     y.float().sum().backward()
     assert layer.weight.grad is not None and layer.weight.grad.dtype == torch.float32
     assert torch.isfinite(layer.weight.grad).all() and x.grad is not None
-
-
-def test_writes_through_data_are_seen_by_the_cached_paths(oracle):
-    """`p.data.copy_(w)` bumps no version counter.  Every cached path must still use the new weights on the next
-    inference-mode forward: the training modules (packed copy of the master), the inference module (tiled copy of
-    the packed buffer) and the decoder's fused sibling layers."""
-    import bittorch_b200 as bt
-    from bittorch_b200.utils.decoder import _FusedColumns
-
-    g = torch.Generator().manual_seed(7)
-    k, n = 256, 96
-    w0, w1 = torch.randn(n, k, generator=g).cuda(), torch.randn(n, k, generator=g).cuda()
-    x = torch.randn(3, k, generator=g).cuda()
-    for cls in (bt.nn.TernaryLinear, bt.nn.TernaryLinearCUDA):
-        layer = cls(k, n, bias=False).cuda() if cls is bt.nn.TernaryLinearCUDA else cls(k, n, bias=False, backend="cuda").cuda()
-        with torch.no_grad():
-            layer.weight.data.copy_(w0)
-            y0 = layer(x)
-            assert torch.equal(layer(x), y0)                          # served from the cache
-            version = layer.weight._version
-            layer.weight.data.copy_(w1)
-            assert layer.weight._version == version                   # the write the version counter cannot see
-            y1 = layer(x)
-        codes, scale = oracle.ternarize(w1.cpu().numpy(), 0.05)
-        assert np.array_equal(y1.cpu().numpy().view(np.uint32),
-                              _oracle_int8_forward(oracle, x.cpu().numpy(), codes, scale, None).view(np.uint32))
-        assert not torch.equal(y0, y1)
-
-    a = bt.nn.create_ternary_linear_inference(k, n, w0, None)
-    b = bt.nn.create_ternary_linear_inference(k, n, w1, None)
-    ya, yb = a(x), b(x)
-    a.weight_packed.data.copy_(b.weight_packed)
-    a.scale.data.copy_(b.scale)
-    assert torch.equal(a(x), yb) and not torch.equal(ya, yb)
-
-    # with the content check off only the explicit call helps
-    c = bt.nn.create_ternary_linear_inference(k, n, w0, None)
-    c.verify_buffers = False
-    yc = c(x)
-    c.weight_packed.data.copy_(b.weight_packed)
-    assert torch.equal(c(x), yc)                                      # stale by construction
-    c.invalidate_cache()
-    want = bt.nn.TernaryLinearInference(k, n, b.weight_packed.clone(), c.scale.clone())(x)
-    assert torch.equal(c(x), want) and not torch.equal(want, yc)
-
-    # fused sibling layers follow their members
-    m1 = bt.nn.create_ternary_linear_inference(k, n, w0, None)
-    m2 = bt.nn.create_ternary_linear_inference(k, 32, w1[:32].contiguous(), None)
-    fused = _FusedColumns(m1, m2)
-    o1, o2 = fused(x)
-    assert torch.equal(o1, m1(x)) and torch.equal(o2, m2(x))          # one launch == the members, bit for bit
-    m1.weight_packed.data.copy_(b.weight_packed)
-    m1.scale.data.copy_(b.scale)
-    o1, o2 = fused(x)
-    assert torch.equal(o1, yb) and torch.equal(o2, m2(x))
-
-
-def test_float64_inputs_run_the_float_path(oracle):
-    """The reference dispatches its float kernels for float64 too (AT_DISPATCH_FLOATING_TYPES_AND_HALF) and computes in
-    float32 (tests/test_gradient_consistency.py:233-237 feeds float64): same here, through the unpacked entry, the
-    packed entry and the training module's forward and backward."""
-    import bittorch_b200 as bt
-    from bittorch_b200 import _C
-
-    g = torch.Generator().manual_seed(9)
-    k, n = 40, 24
-    w = torch.randn(n, k, generator=g, dtype=torch.float64)
-    x = torch.randn(5, k, generator=g, dtype=torch.float64)
-    bias = torch.randn(n, generator=g, dtype=torch.float64)
-    codes, scale = oracle.ternarize(w.float().numpy(), 0.05)
-    y_ref = oracle.linear_float(x.float().numpy(), codes, scale, bias.float().numpy())
-    y = _C.ternary_linear_forward(x.cuda(), torch.from_numpy(codes).cuda(), torch.from_numpy(scale).double().cuda(), bias.cuda())
-    assert y.dtype == torch.float64 and np.allclose(y.cpu().numpy(), y_ref, rtol=1e-4, atol=1e-4)
-    packed = _C.pack_codes(torch.from_numpy(codes).cuda())
-    y = _C.ternary_linear_packed_forward(x.cuda(), packed, torch.from_numpy(scale).double().cuda(), bias.cuda(), k)
-    assert y.dtype == torch.float64 and np.allclose(y.cpu().numpy(), y_ref, rtol=1e-4, atol=1e-4)
-
-    ref = bt.nn.TernaryLinear(k, n, backend="python").double().cuda()
-    cu = bt.nn.TernaryLinear(k, n, backend="cuda").double().cuda()
-    cu.load_state_dict(ref.state_dict())
-    x1, x2 = x.cuda().clone().requires_grad_(True), x.cuda().clone().requires_grad_(True)
-    y1, y2 = ref(x1), cu(x2)
-    assert y2.dtype == torch.float64 and torch.allclose(y1, y2, rtol=1e-4, atol=1e-5)      # float32 arithmetic inside
-    gy = torch.randn(5, n, generator=g, dtype=torch.float64).cuda()
-    y1.backward(gy)
-    y2.backward(gy)
-    assert torch.allclose(x1.grad, x2.grad, rtol=1e-6, atol=1e-8)
-    assert torch.allclose(ref.weight.grad, cu.weight.grad, rtol=1e-6, atol=1e-8)
-
-
-def test_a_wait_that_runs_out_is_reported_and_the_context_stays_usable():
-    """The give-up path of the library's bounded device-side waits, through its self-test kernel (a barrier that
-    nothing arrives on, a few thousand polls): the kernel returns, the status word reads BT_ERR_DEVICE_WAIT once and
-    is clear afterwards, and the next kernel runs normally.  Nothing faults or traps."""
-    from bittorch_b200 import _C
-
-    assert _C.device_status() == 0
-    _C.selftest_wait_timeout()
-    assert _C.device_status() == 4
-    assert _C.device_status() == 0
-    x = torch.arange(12, dtype=torch.float32).reshape(3, 4).cuda()
-    assert torch.equal(_C.dummy(x), x)
-    assert _C.device_status() == 0

@@ -160,24 +160,3 @@ def test_quant_api_matches_reference_semantics():
     t_ste.sum().backward()
     assert torch.equal(w2.grad, torch.ones_like(w2))       # tests/test_ternary_quant.py:103-116
     assert quant.get_packed_size(4096, 4096) == 4 * 1024 * 1024
-
-
-def test_row_layout_packer_and_unpacker(oracle):
-    """pack_ternary / unpack_ternary ([N, ceil(K/4)], bittorch/quant/ternary_packed.py:22-120) as kernels of their
-    own: the oracle's bytes, the docstring's known answer, ragged K, the reserved pattern."""
-    import bittorch_b200 as bt
-
-    kat = torch.tensor([[1, -1, 0, 1], [0, 1, 1, -1]], dtype=torch.float32).cuda()
-    packed, k = bt.quant.pack_ternary(kat)
-    assert k == 4 and packed.cpu().tolist() == [[73], [148]]                 # 0x49 and its neighbour
-    for (n, k) in [(1, 1), (5, 7), (33, 130), (64, 256), (17, 1023)]:
-        g = torch.Generator().manual_seed(n * 1000 + k)
-        codes = torch.randint(-1, 2, (n, k), generator=g, dtype=torch.int8)
-        packed, k_out = bt.quant.pack_ternary(codes.cuda())
-        assert k_out == k and packed.shape == (n, (k + 3) // 4) and packed.dtype == torch.uint8
-        assert np.array_equal(packed.cpu().numpy(), oracle.pack(codes.numpy()))
-        back = bt.quant.unpack_ternary(packed, k)
-        assert back.dtype == torch.int8 and torch.equal(back.cpu(), codes)
-        assert torch.equal(packed.T.contiguous(), bt.quant.pack_ternary_transposed(codes.cuda())[0])
-    reserved = torch.full((3, 2), 0xFF, dtype=torch.uint8).cuda()
-    assert int(bt.quant.unpack_ternary(reserved, 8).abs().sum()) == 0       # pattern 11 decodes to 0
