@@ -57,6 +57,8 @@ _SIGNATURES = {
     "bt_gemv_tiled_chained": ([_p, _int, _i64, _i64, _i64, _p, _i64, _p, _p, _p, _int, _i64, _p, _p, _i64, _int, _p], _int),
     "bt_gemv_tiled_float": ([_p, _int, _i64, _i64, _i64, _p, _i64, _p, _p, _p, _int, _i64, _int, _p], _int),
     "bt_gemm_tiled_i8": ([_p, _p, _p, _i64, _i64, _p, _i64, _p, _p, _p, _int, _i64, _p, _p], _int),
+    "bt_silu_mul_quant": ([_p, _int, _i64, _i64, _i64, _p, _p, _p, _p, _p], _int),
+    "bt_add_rmsnorm_quant": ([_p, _p, _int, _i64, _i64, _i64, _i64, _p, _f32, _p, _p, _p, _p, _p], _int),
     "bt_linear_unpacked": ([_p, _int, _i64, _i64, _p, _i64, _p, _p, _p, _p], _int),
     "bt_linear_packed_float": ([_p, _int, _i64, _i64, _p, _i64, _p, _p, _p, _p], _int),
 }
@@ -245,6 +247,53 @@ def act_quant_i8(x2d: Tensor, want_sum: bool = False):
         _check(_lib.bt_act_quant_i8(_ptr(x2d), _dtype_code(x2d, "X"), m, k, x2d.stride(0), _ptr(xq), _ptr(sx), _ptr(xsum),
                                     _stream(x2d)))
     return (xq, sx, xsum) if want_sum else (xq, sx)
+
+
+def silu_mul_quant(gate_up: Tensor, want_h: bool = False):
+    """``silu(gate) * up`` of a fused gate/up output [M, 2F] (gate | up), quantized per row in the same kernel:
+    (int8 [M, F], float32 scales [M], int32 row sums [M]) and, with ``want_h``, the unquantized product [M, F]."""
+    _require_cuda(gate_up)
+    if gate_up.dim() != 2 or gate_up.shape[1] % 2:
+        raise RuntimeError("gate_up must be 2D [M, 2F]")
+    if gate_up.stride(1) != 1:
+        gate_up = gate_up.contiguous()
+    m, f = gate_up.shape[0], gate_up.shape[1] // 2
+    dev = gate_up.device
+    hq = torch.empty((m, f), dtype=torch.int8, device=dev)
+    sx = torch.empty((m,), dtype=torch.float32, device=dev)
+    xsum = torch.empty((m,), dtype=torch.int32, device=dev)
+    h = torch.empty((m, f), dtype=gate_up.dtype, device=dev) if want_h else None
+    with torch.cuda.device(dev):
+        _check(_lib.bt_silu_mul_quant(_ptr(gate_up), _dtype_code(gate_up, "gate_up"), m, f, gate_up.stride(0), _ptr(hq),
+                                      _ptr(sx), _ptr(xsum), _ptr(h), _stream(gate_up)))
+    return (hq, sx, xsum, h) if want_h else (hq, sx, xsum)
+
+
+def add_rmsnorm_quant(x2d: Tensor, delta: Optional[Tensor], weight: Tensor, eps: float, want_y: bool = False):
+    """``x2d += delta`` IN PLACE (``delta`` may be None), RMS-normalise with ``weight`` and quantize per row in one
+    kernel: (int8 [M, D], float32 scales [M], int32 row sums [M]) and, with ``want_y``, the normalised rows."""
+    _require_cuda(x2d, weight)
+    if x2d.dim() != 2 or x2d.stride(1) != 1:
+        raise RuntimeError("x2d must be 2D with contiguous rows (it is updated in place)")
+    m, d = x2d.shape
+    if delta is not None:
+        if delta.shape != x2d.shape or delta.dtype != x2d.dtype:
+            raise RuntimeError("delta must have the shape and dtype of x2d")
+        if delta.stride(1) != 1:
+            delta = delta.contiguous()
+    w = weight.detach().to(x2d.dtype).contiguous()
+    if w.shape != (d,):
+        raise RuntimeError("weight must be [D]")
+    dev = x2d.device
+    yq = torch.empty((m, d), dtype=torch.int8, device=dev)
+    sx = torch.empty((m,), dtype=torch.float32, device=dev)
+    xsum = torch.empty((m,), dtype=torch.int32, device=dev)
+    y = torch.empty((m, d), dtype=x2d.dtype, device=dev) if want_y else None
+    with torch.cuda.device(dev):
+        _check(_lib.bt_add_rmsnorm_quant(_ptr(x2d), _ptr(delta), _dtype_code(x2d, "x"), m, d, x2d.stride(0),
+                                         0 if delta is None else delta.stride(0), _ptr(w), float(eps), _ptr(yq), _ptr(sx),
+                                         _ptr(xsum), _ptr(y), _stream(x2d)))
+    return (yq, sx, xsum, y) if want_y else (yq, sx, xsum)
 
 
 def tiled_bytes(in_features: int, out_features: int) -> int:

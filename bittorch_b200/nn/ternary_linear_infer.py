@@ -121,6 +121,25 @@ class TernaryLinearInference(nn.Module):
         y = C.int8_linear_tiled(x2d, tiled, self.in_features, self.out_features, s32, b32, fresh_weights=fresh)
         return y.reshape(*x.shape[:-1], self.out_features)
 
+    def forward_quantized(self, xq: Tensor, sx: Tensor, xsum: Optional[Tensor], out_dtype: torch.dtype) -> Tensor:
+        """The layer on activations that are already int8 rows [M, in_features] with per-row scales (and row sums),
+        as ``act_quant_i8`` or the fused elementwise kernels (``add_rmsnorm_quant``, ``silu_mul_quant``) emit them
+        -> [M, out_features] in ``out_dtype``.  Same arithmetic as ``forward`` on the integer path."""
+        C = require_ext()
+        if xq.dim() != 2 or xq.shape[1] != self.in_features or xq.dtype != torch.int8:
+            raise RuntimeError("xq must be int8 [M, in_features]")
+        tiled, s32, b32, fresh = self._derived()
+        m, k, n = xq.shape[0], self.in_features, self.out_features
+        if m <= C.DECODE_MAX_M:
+            return C.gemv_tiled_i8(xq, sx, tiled, k, n, s32, b32, out_dtype, fresh_weights=fresh)
+        if k % 16 == 0:
+            return C.gemm_tiled_i8(xq, sx, tiled, k, n, s32, b32, out_dtype, xsum=xsum)
+        y = torch.empty((m, n), dtype=out_dtype, device=xq.device)        # ragged K: the decode kernel, 16 rows at a time
+        for m0 in range(0, m, C.GEMV_MAX_M):
+            m1 = min(m, m0 + C.GEMV_MAX_M)
+            C.gemv_tiled_i8(xq[m0:m1], sx[m0:m1], tiled, k, n, s32, b32, out_dtype, out=y[m0:m1], fresh_weights=fresh)
+        return y
+
     def extra_repr(self) -> str:
         packed_bytes = self.packed_size_bytes
         reduction = (self.out_features * self.in_features * 4) / (packed_bytes + self.scale.numel() * 2)

@@ -56,6 +56,7 @@ class DecoderConfig:
     threshold_factor: float = 0.05
     backend: str = "auto"
     one_weight_copy: bool = True              # inference form: keep only the tiled copy of every projection on the device
+    fused_elementwise: bool = True            # inference form, integer path: residual add + RMSNorm and SiLU * up run inside the quantizer kernels
 
     def __post_init__(self) -> None:
         if self.n_kv_heads is None:
@@ -173,11 +174,15 @@ class _FusedColumns:
             return key + self._key[len(key):]
         return key
 
-    def __call__(self, x: Tensor):
+    def fused(self) -> TernaryLinearInference:
+        """The fused layer, rebuilt if a member changed."""
         if self._members_key() != self._key:
             self._fused = fuse_inference_columns(self.layers, share=self.share)
             self._key = self._members_key()                   # after fusing: sharing replaces the members' buffers
-        return torch.split(self._fused(x), [l.out_features for l in self.layers], dim=-1)
+        return self._fused
+
+    def __call__(self, x: Tensor):
+        return torch.split(self.fused()(x), [l.out_features for l in self.layers], dim=-1)
 
 
 class Attention(nn.Module):
@@ -191,26 +196,33 @@ class Attention(nn.Module):
         self.proj = mk(cfg.dim, cfg.dim)
         self._fused: Optional[_FusedColumns] = None
 
-    def _qkv(self, x: Tensor):
-        """x [B, T, dim] -> q [B, H, T, hd], k and v [B, Hkv, T, hd] (not yet rotated)."""
-        cfg = self.cfg
-        b, t, _ = x.shape
-        hd, nh, nkv = cfg.head_dim, cfg.n_heads, cfg.n_kv_heads
+    def fused_columns(self) -> _FusedColumns:
         if self._fused is None or self._fused.layers != (self.q_proj, self.kv_proj):
-            self._fused = _FusedColumns(self.q_proj, self.kv_proj, share=cfg.one_weight_copy)
-        if self._fused.usable:                           # packed layers: one launch for both projections
-            q, kv = self._fused(x)
-        else:
-            q, kv = self.q_proj(x), self.kv_proj(x)
-        q = q.reshape(b, t, nh, hd).transpose(1, 2)
-        kv = kv.reshape(b, t, 2, nkv, hd)
+            self._fused = _FusedColumns(self.q_proj, self.kv_proj, share=self.cfg.one_weight_copy)
+        return self._fused
+
+    def _heads(self, q: Tensor, kv: Tensor, b: int, t: int):
+        """flat projections -> q [B, H, T, hd], k and v [B, Hkv, T, hd] (not yet rotated)."""
+        cfg = self.cfg
+        q = q.reshape(b, t, cfg.n_heads, cfg.head_dim).transpose(1, 2)
+        kv = kv.reshape(b, t, 2, cfg.n_kv_heads, cfg.head_dim)
         return q, kv[:, :, 0].transpose(1, 2), kv[:, :, 1].transpose(1, 2)
 
-    def forward(self, x: Tensor, cache: Tuple[Tensor, Tensor], pos0: int, cos: Tensor, sin: Tensor) -> Tensor:
-        cfg = self.cfg
+    def _qkv(self, x: Tensor):
         b, t, _ = x.shape
-        hd, nh, nkv = cfg.head_dim, cfg.n_heads, cfg.n_kv_heads
-        q, k, v = self._qkv(x)
+        fused = self.fused_columns()
+        if fused.usable:                                 # packed layers: one launch for both projections
+            q, kv = fused(x)
+        else:
+            q, kv = self.q_proj(x), self.kv_proj(x)
+        return self._heads(q, kv, b, t)
+
+    def _attend(self, q: Tensor, k: Tensor, v: Tensor, cache: Tuple[Tensor, Tensor], pos0: int, cos: Tensor,
+                sin: Tensor) -> Tensor:
+        """Rotary embedding, cache update and causal attention for T tokens at positions pos0 .. -> [B, T, dim]."""
+        cfg = self.cfg
+        b, _, t, hd = q.shape
+        nh, nkv = cfg.n_heads, cfg.n_kv_heads
         q = apply_rope(q, cos, sin, pos0)
         k_cache, v_cache = cache                                                 # [B, Hkv, max_seq_len, hd]
         k_cache[:, :, pos0:pos0 + t] = apply_rope(k, cos, sin, pos0).to(k_cache.dtype)   # keys are stored rotated
@@ -221,20 +233,20 @@ class Attention(nn.Module):
             keys = keys.repeat_interleave(nh // nkv, dim=1)                      # query head h reads kv head h // group
             vals = vals.repeat_interleave(nh // nkv, dim=1)
         # query at position pos0 + i sees keys 0 .. pos0 + i
-        mask = torch.ones(t, pos0 + t, dtype=torch.bool, device=x.device).tril(diagonal=pos0)
+        mask = torch.ones(t, pos0 + t, dtype=torch.bool, device=q.device).tril(diagonal=pos0)
         out = F.scaled_dot_product_attention(q, keys, vals, attn_mask=mask, scale=1.0 / math.sqrt(hd))
-        return self.proj(out.transpose(1, 2).reshape(b, t, cfg.dim))
+        return out.transpose(1, 2).reshape(b, t, cfg.dim)
 
-    def decode_step(self, x: Tensor, cache: Tuple[Tensor, Tensor], pos: Tensor, cos: Tensor, sin: Tensor) -> Tensor:
-        """One token per sequence at the position in the device tensor ``pos`` [1] (int64): x [B, 1, dim].  Every
-        shape is independent of the position: the new key/value go into the cache with ``index_copy_`` and the
-        query attends over the WHOLE cache with the positions after ``pos`` masked out.  The query heads of one
-        key/value head are batched against it ([B, Hkv, group, hd] x [B, Hkv, S, hd]), so grouped-query attention
-        copies nothing."""
+    def _attend_fixed(self, q: Tensor, k: Tensor, v: Tensor, cache: Tuple[Tensor, Tensor], pos: Tensor, cos: Tensor,
+                      sin: Tensor) -> Tensor:
+        """The same for ONE token per sequence at the position in the device tensor ``pos`` [1] (int64), with every
+        shape independent of the position: the new key/value go into the cache with ``index_copy_`` and the query
+        attends over the WHOLE cache with the positions after ``pos`` masked out.  The query heads of one key/value
+        head are batched against it ([B, Hkv, group, hd] x [B, Hkv, S, hd]), so grouped-query attention copies
+        nothing.  -> [B, 1, dim]"""
         cfg = self.cfg
-        b = x.shape[0]
+        b = q.shape[0]
         hd, nh, nkv = cfg.head_dim, cfg.n_heads, cfg.n_kv_heads
-        q, k, v = self._qkv(x)
         q = apply_rope_at(q, cos, sin, pos)
         k_cache, v_cache = cache
         k_cache.index_copy_(2, pos, apply_rope_at(k, cos, sin, pos).to(k_cache.dtype))
@@ -242,10 +254,19 @@ class Attention(nn.Module):
         seq = k_cache.shape[2]
         qg = q.reshape(b, nkv, nh // nkv, hd)                                    # query head h = kv head * group + g
         scores = torch.matmul(qg, k_cache.to(q.dtype).transpose(2, 3)) * (1.0 / math.sqrt(hd))     # [B, Hkv, group, S]
-        visible = torch.arange(seq, device=x.device) <= pos                      # [S]
+        visible = torch.arange(seq, device=q.device) <= pos                      # [S]
         scores = scores.float().masked_fill(~visible, float("-inf"))
         out = torch.matmul(torch.softmax(scores, dim=-1).to(q.dtype), v_cache.to(q.dtype))          # [B, Hkv, group, hd]
-        return self.proj(out.reshape(b, 1, cfg.dim))
+        return out.reshape(b, 1, cfg.dim)
+
+    def forward(self, x: Tensor, cache: Tuple[Tensor, Tensor], pos0: int, cos: Tensor, sin: Tensor) -> Tensor:
+        q, k, v = self._qkv(x)
+        return self.proj(self._attend(q, k, v, cache, pos0, cos, sin))
+
+    def decode_step(self, x: Tensor, cache: Tuple[Tensor, Tensor], pos: Tensor, cos: Tensor, sin: Tensor) -> Tensor:
+        """One token per sequence (x [B, 1, dim]) at the position in the device tensor ``pos``: fixed shapes."""
+        q, k, v = self._qkv(x)
+        return self.proj(self._attend_fixed(q, k, v, cache, pos, cos, sin))
 
 
 class SwiGLU(nn.Module):
@@ -258,11 +279,15 @@ class SwiGLU(nn.Module):
         self.cfg = cfg
         self._fused: Optional[_FusedColumns] = None
 
-    def forward(self, x: Tensor) -> Tensor:
+    def fused_columns(self) -> _FusedColumns:
         if self._fused is None or self._fused.layers != (self.w_gate, self.w_up):
             self._fused = _FusedColumns(self.w_gate, self.w_up, share=self.cfg.one_weight_copy)
-        if self._fused.usable:                           # packed layers: one launch for gate and up
-            gate, up = self._fused(x)
+        return self._fused
+
+    def forward(self, x: Tensor) -> Tensor:
+        fused = self.fused_columns()
+        if fused.usable:                                 # packed layers: one launch for gate and up
+            gate, up = fused(x)
         else:
             gate, up = self.w_gate(x), self.w_up(x)
         return self.w_down(F.silu(gate) * up)
@@ -283,6 +308,42 @@ class Block(nn.Module):
     def decode_step(self, x: Tensor, cache, pos: Tensor, cos: Tensor, sin: Tensor) -> Tensor:
         x = x + self.attn.decode_step(self.norm1(x), cache, pos, cos, sin)
         return x + self.mlp(self.norm2(x))
+
+    def fused_elementwise_ok(self) -> bool:
+        """The block can run with its elementwise steps inside the quantizer kernels: every projection packed, the
+        integer activation path selected."""
+        from .._ext import require_ext
+
+        layers = (self.attn.q_proj, self.attn.kv_proj, self.attn.proj, self.mlp.w_gate, self.mlp.w_up, self.mlp.w_down)
+        return (self.attn.cfg.fused_elementwise and all(isinstance(l, TernaryLinearInference) for l in layers)
+                and require_ext().activation_mode() == "int8")
+
+    def forward_fused(self, x: Tensor, delta: Optional[Tensor], cache, pos, cos: Tensor, sin: Tensor, fixed: bool):
+        """The block with its elementwise steps fused into the activation quantizer, so that every packed layer but
+        ``proj`` starts from int8 rows (``bt_add_rmsnorm_quant``, ``bt_silu_mul_quant``):
+
+            x += delta; q8 = quant(norm1(x))  ->  q, kv = [q_proj | kv_proj](q8)  ->  attention  ->  a = proj(.)
+            x += a;     q8 = quant(norm2(x))  ->  gu = [w_gate | w_up](q8)  ->  h8 = quant(silu(gate) * up)  ->  d = w_down(h8)
+
+        ``x`` [B, T, dim] is the residual stream, updated IN PLACE; ``delta`` is what the previous block's MLP still
+        owes it (None for the first block).  Returns (x, d): the caller (next block, or the final norm) adds d.
+        ``fixed``: one token at the position in the device tensor ``pos``; else T tokens from the integer ``pos``."""
+        from .._ext import require_ext
+
+        C = require_ext()
+        b, t, d = x.shape
+        x2d = x.view(b * t, d)
+        xq, sx, xsum = C.add_rmsnorm_quant(x2d, None if delta is None else delta.reshape(b * t, d), self.norm1.weight, NORM_EPS)
+        attn = self.attn
+        qkv = attn.fused_columns().fused().forward_quantized(xq, sx, xsum, x.dtype)
+        q, k, v = attn._heads(qkv[:, :attn.q_proj.out_features], qkv[:, attn.q_proj.out_features:], b, t)
+        out = attn._attend_fixed(q, k, v, cache, pos, cos, sin) if fixed else attn._attend(q, k, v, cache, pos, cos, sin)
+        a = attn.proj(out)
+        xq, sx, xsum = C.add_rmsnorm_quant(x2d, a.reshape(b * t, d), self.norm2.weight, NORM_EPS)
+        gate_up = self.mlp.fused_columns().fused().forward_quantized(xq, sx, xsum, x.dtype)     # [M, gate | up]
+        hq, sh, hsum = C.silu_mul_quant(gate_up)
+        down = self.mlp.w_down.forward_quantized(hq, sh, hsum, x.dtype)
+        return x, down.view(b, t, d)
 
 
 class TernaryDecoder(nn.Module):
@@ -317,14 +378,28 @@ class TernaryDecoder(nn.Module):
                 raise ValueError("a pass that does not start at position 0 needs the cache of the earlier positions")
             cache = self.new_cache(b)
         x = self.tok(tokens)
+        if self._fused_blocks():
+            return self._run_fused(x, cache, pos0, fixed=False)
         for block, layer_cache in zip(self.blocks, cache):
             x = block(x, layer_cache, pos0, self.rope_cos, self.rope_sin)
         return self.head(self.norm(x))
+
+    def _fused_blocks(self) -> bool:
+        return len(self.blocks) > 0 and all(block.fused_elementwise_ok() for block in self.blocks)
+
+    def _run_fused(self, x: Tensor, cache: list, pos, fixed: bool) -> Tensor:
+        x = x.contiguous()                                     # the embedding's output: a fresh tensor, updated in place
+        delta = None
+        for block, layer_cache in zip(self.blocks, cache):
+            x, delta = block.forward_fused(x, delta, layer_cache, pos, self.rope_cos, self.rope_sin, fixed)
+        return self.head(self.norm(x + delta))
 
     def decode_step(self, tokens: Tensor, cache: list, pos: Tensor) -> Tensor:
         """tokens [B, 1] at the position held in the device tensor ``pos`` [1] (int64) -> logits [B, 1, vocab].
         Same result as ``forward(tokens, cache, int(pos))``, with shapes that do not depend on the position."""
         x = self.tok(tokens)
+        if self._fused_blocks():
+            return self._run_fused(x, cache, pos, fixed=True)
         for block, layer_cache in zip(self.blocks, cache):
             x = block.decode_step(x, layer_cache, pos, self.rope_cos, self.rope_sin)
         return self.head(self.norm(x))

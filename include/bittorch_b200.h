@@ -276,6 +276,32 @@ int bt_gemm_tiled_i8(const int8_t* Xq, const float* sx, const int32_t* xsum, int
                      void* Y, int y_dtype, int64_t ldy, int32_t* acc_out, void* stream);
 
 /*
+ * Elementwise steps of a decoder block fused with the per-token int8 quantizer of
+ * bt_act_quant_i8, so that the packed layer behind them starts from int8 rows + scales
+ * (bt_gemv_tiled_i8 / bt_gemm_tiled_i8).  No counterpart in the reference's Python
+ * package; the steps are those of its browser runtime (SwiGLU:
+ * js/src/models/TernaryTransformer.ts:520-550; pre-norm residual block: :366-464; RMSNorm
+ * with eps inside the root: js/src/core/RMSNorm.ts:10-38).  Values are rounded to the
+ * activation type `dtype` wherever the unfused sequence of operations would have stored
+ * them; the arithmetic is fixed operation by operation (see csrc/fused_elementwise.cuh), so
+ * results do not depend on the launch.
+ *
+ * bt_silu_mul_quant:    h = silu(gate) * up.  GU [M, ld] holds gate in columns [0, F) and up
+ *                       in [F, 2F) (the output of a fused gate/up layer).  Hq int8 [M, F],
+ *                       sx float32 [M], xsum int32 [M] or NULL, H [M, F] in dtype or NULL
+ *                       (the unquantized product).
+ * bt_add_rmsnorm_quant: x += delta (delta NULL: no addition); y = x / sqrt(mean(x^2) + eps)
+ *                       * weight.  X [M, ldx] is UPDATED IN PLACE (the residual stream),
+ *                       delta [M, ldd], weight [D] in dtype.  Yq int8 [M, D], sx, xsum as
+ *                       above, Y [M, D] in dtype or NULL (the unquantized normalised row).
+ */
+int bt_silu_mul_quant(const void* GU, int dtype, int64_t M, int64_t F, int64_t ld,
+                      int8_t* Hq, float* sx, int32_t* xsum, void* H, void* stream);
+int bt_add_rmsnorm_quant(void* X, const void* delta, int dtype, int64_t M, int64_t D,
+                         int64_t ldx, int64_t ldd, const void* weight, float eps,
+                         int8_t* Yq, float* sx, int32_t* xsum, void* Y, void* stream);
+
+/*
  * Unpacked-weight linear with floating-point activations, fp32 accumulation:
  *   Y[b,n] = (sum_k X[b,k] * W[n,k]) * scale[n] + bias[n],   W int8 [N,K]
  * Replaces `_C.ternary_linear_forward` (csrc/core/dispatch.cpp:52-87;

@@ -22,4 +22,7 @@ from .oracle import (  # noqa: F401
     packed_forward_i8,
     packed_forward_i8_threaded,
     ref_python_forward,
+    silu_mul_quant,
+    add_rmsnorm_quant,
+    exp_plain,
 )

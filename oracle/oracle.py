@@ -52,9 +52,14 @@ def _load():
             lib.bto_epilogue.argtypes = [_p, _i64, _i64, _p, _p, _p, _p]
             lib.bto_linear_float.argtypes = [_p, _i64, _i64, _p, _i64, _p, _p, _p]
             lib.bto_packed_forward_i8.argtypes = [_p, _p, _i64, _i64, _p, _i64, _i64, _i64, _p, _p, _p]
+            lib.bto_silu_mul_quant.argtypes = [_p, _i64, _i64, _i64, _int, _p, _p, _p, _p]
+            lib.bto_add_rmsnorm_quant.argtypes = [_p, _p, _i64, _i64, _i64, _i64, _p, _f32, _int, _p, _p, _p, _p]
+            lib.bto_exp_plain.argtypes = [_f32]
+            lib.bto_exp_plain.restype = _f32
             for name in (
                 "bto_ternarize", "bto_pack", "bto_pack_transposed", "bto_unpack", "bto_unpack_transposed",
                 "bto_act_quant", "bto_gemm_i32", "bto_epilogue", "bto_linear_float", "bto_packed_forward_i8",
+                "bto_silu_mul_quant", "bto_add_rmsnorm_quant",
             ):
                 getattr(lib, name).restype = None
             _lib = lib
@@ -197,6 +202,36 @@ def packed_forward_i8_threaded(x, packed_t, k: int, scale, bias=None, threads: i
         for f in futs:
             f.result()
     return y
+
+
+def silu_mul_quant(gate_up, dtype: int = DT_F32):
+    """(int8 h [M,F], sx [M], row sums [M], h float32 [M,F]) of ``silu(gate) * up`` for gate_up [M, 2F] (values
+    already representable in ``dtype``) - the definition the fused kernel is pinned to."""
+    gu = _c(gate_up, np.float32)
+    m, f2 = gu.shape
+    f = f2 // 2
+    hq, sx, xsum = np.empty((m, f), np.int8), np.empty(m, np.float32), np.empty(m, np.int32)
+    h = np.empty((m, f), np.float32)
+    _load().bto_silu_mul_quant(_ptr(gu), m, f, f2, dtype, _ptr(hq), _ptr(sx), _ptr(xsum), _ptr(h))
+    return hq, sx, xsum, h
+
+
+def add_rmsnorm_quant(x, delta, weight, eps: float, dtype: int = DT_F32):
+    """(new x [M,D], int8 y, sx, row sums, y float32) of ``x += delta; y = x / rms(x) * weight`` followed by the
+    per-row quantizer; ``delta`` may be None."""
+    x = np.array(x, np.float32, copy=True, order="C")
+    m, d = x.shape
+    delta = None if delta is None else _c(delta, np.float32)
+    w = _c(weight, np.float32)
+    yq, sx, xsum = np.empty((m, d), np.int8), np.empty(m, np.float32), np.empty(m, np.int32)
+    y = np.empty((m, d), np.float32)
+    _load().bto_add_rmsnorm_quant(_ptr(x), _ptr(delta), m, d, d, d, _ptr(w), np.float32(eps), dtype, _ptr(yq), _ptr(sx),
+                                  _ptr(xsum), _ptr(y))
+    return x, yq, sx, xsum, y
+
+
+def exp_plain(x: float) -> float:
+    return float(_load().bto_exp_plain(np.float32(x)))
 
 
 def ref_python_forward(x, weight, bias=None, threshold_factor: float = 0.05):

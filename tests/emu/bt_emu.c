@@ -467,6 +467,48 @@ int bt_gemm_tiled_i8(const int8_t* Xq, const float* sx, const int32_t* xsum, int
     return rc;
 }
 
+int bt_silu_mul_quant(const void* GU, int dtype, int64_t M, int64_t F, int64_t ld, int8_t* Hq, float* sx, int32_t* xsum,
+                      void* H, void* stream) {
+    (void)stream;
+    REQUIRE(GU && Hq && sx, "bt_silu_mul_quant: NULL pointer");
+    REQUIRE(valid_dtype(dtype), "bt_silu_mul_quant: unknown dtype %d", dtype);
+    REQUIRE(M > 0 && F > 0, "bt_silu_mul_quant: input is empty");
+    REQUIRE(ld >= 2 * F, "bt_silu_mul_quant: row stride < 2F");
+    float* gu = widen(GU, dtype, M, 2 * F, ld);
+    float* h = H ? (float*)malloc(sizeof(float) * (size_t)(M * F)) : NULL;
+    bto_silu_mul_quant(gu, M, F, 2 * F, dtype, Hq, sx, xsum, h);
+    if (H)
+        for (int64_t i = 0; i < M * F; ++i) store_elem(H, dtype, i, h[i]);
+    free(gu);
+    free(h);
+    return BT_OK;
+}
+
+int bt_add_rmsnorm_quant(void* X, const void* delta, int dtype, int64_t M, int64_t D, int64_t ldx, int64_t ldd,
+                         const void* weight, float eps, int8_t* Yq, float* sx, int32_t* xsum, void* Y, void* stream) {
+    (void)stream;
+    REQUIRE(X && weight && Yq && sx, "bt_add_rmsnorm_quant: NULL pointer");
+    REQUIRE(valid_dtype(dtype), "bt_add_rmsnorm_quant: unknown dtype %d", dtype);
+    REQUIRE(M > 0 && D > 0, "bt_add_rmsnorm_quant: input is empty");
+    REQUIRE(ldx >= D && (!delta || ldd >= D), "bt_add_rmsnorm_quant: row stride smaller than D");
+    REQUIRE(eps >= 0.0f, "bt_add_rmsnorm_quant: eps must not be negative");
+    float* x = widen(X, dtype, M, D, ldx);
+    float* d = delta ? widen(delta, dtype, M, D, ldd) : NULL;
+    float* w = widen(weight, dtype, 1, D, D);
+    float* y = Y ? (float*)malloc(sizeof(float) * (size_t)(M * D)) : NULL;
+    bto_add_rmsnorm_quant(x, d, M, D, D, D, w, eps, dtype, Yq, sx, xsum, y);
+    if (delta)
+        for (int64_t m = 0; m < M; ++m)
+            for (int64_t k = 0; k < D; ++k) store_elem(X, dtype, m * ldx + k, x[m * D + k]);
+    if (Y)
+        for (int64_t i = 0; i < M * D; ++i) store_elem(Y, dtype, i, y[i]);
+    free(x);
+    free(d);
+    free(w);
+    free(y);
+    return BT_OK;
+}
+
 static int float_linear(const void* X, int x_dtype, int64_t M, int64_t K, const int8_t* codes, int64_t N,
                         const float* scale, const float* bias, void* Y) {
     float* x = widen(X, x_dtype, M, K, K);

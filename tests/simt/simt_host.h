@@ -212,6 +212,8 @@ inline float __int_as_float(int i) { float f; memcpy(&f, &i, 4); return f; }
 inline float __fdiv_rn(float a, float b) { return a / b; }
 inline float __fmul_rn(float a, float b) { return a * b; }            // build with -ffp-contract=off
 inline float __fadd_rn(float a, float b) { return a + b; }
+inline long long __double_as_longlong(double d) { long long v; memcpy(&v, &d, 8); return v; }
+inline double __longlong_as_double(long long v) { double d; memcpy(&d, &v, 8); return d; }
 inline float __int2float_rn(int v) { return static_cast<float>(v); }
 inline float __ll2float_rn(long long v) { return static_cast<float>(v); }
 inline int __float2int_rn(float v) {                                     // round to nearest even, saturating; NaN -> 0

@@ -2,7 +2,8 @@
 //
 // Includes the real kernel files, so every extern "C" entry point they define (bt_quantize_pack, bt_pack_codes[_rows],
 // bt_unpack_codes[_rows], bt_act_quant_i8, bt_retile_packed, bt_untile_packed, bt_gemv_tiled, bt_gemv_tiled_i8,
-// bt_gemv_tiled_chained, bt_gemv_tiled_float, bt_linear_unpacked, bt_linear_packed_float) is exported with its
+// bt_gemv_tiled_chained, bt_gemv_tiled_float, bt_linear_unpacked, bt_linear_packed_float, bt_silu_mul_quant,
+// bt_add_rmsnorm_quant) is exported with its
 // usual signature and takes HOST pointers.  Not built here: the tensor-core GEMMs (tcgen05, TMEM) and the
 // cluster kernel of the public layout (distributed shared memory).
 #include "simt_host.h"
@@ -29,6 +30,7 @@ int tuning(int) { return -1; }
 }  // namespace bt
 
 #include "../../bittorch_b200/csrc/act_quant.cuh"
+#include "../../bittorch_b200/csrc/fused_elementwise.cuh"
 #include "../../bittorch_b200/csrc/gemv_tiled.cuh"
 #include "../../bittorch_b200/csrc/linear_float.cuh"
 #include "../../bittorch_b200/csrc/quantize_pack.cuh"

@@ -294,3 +294,58 @@ def test_the_emulated_hardware_rules_are_enforced(L, oracle):
     y = np.empty((1, n), np.float32)
     rc = L.bt_gemv_tiled_i8(H.ptr(xq), H.ptr(sx), 1, k, H.ptr(bad), n, H.ptr(scale), None, H.ptr(y), H.F32, n, None, 0, None)
     assert rc == 1 and b"16-byte aligned" in L.bt_last_error()
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# decoder-block elementwise steps fused with the quantizer
+# ---------------------------------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("dtype", [H.BF16, H.F32, H.F16])
+@pytest.mark.parametrize("m,f", [(1, 1500), (3, 64), (2, 1), (1, 4096)])
+def test_silu_mul_quant_kernel(L, oracle, m, f, dtype):
+    rng = np.random.default_rng(m * 10 + f + dtype)
+    gu = rng.standard_normal((m, 2 * f + 8)).astype(np.float32) * 4.0          # rows with a stride
+    gu[0, : min(3, f)] = [-90.0, 90.0, 0.0][: min(3, f)]                        # the exponential's clamped ends, zero
+    gub = H.to_bits(gu, dtype)
+    hq, sx, xsum = np.empty((m, f), np.int8), np.empty(m, np.float32), np.empty(m, np.int32)
+    h = H.empty_out((m, f), dtype)
+    H.check(L.bt_silu_mul_quant(H.ptr(gub), dtype, m, f, 2 * f + 8, H.ptr(hq), H.ptr(sx), H.ptr(xsum), H.ptr(h), None))
+    q_ref, sx_ref, sum_ref, h_ref = oracle.silu_mul_quant(H.from_bits(gub, dtype)[:, : 2 * f], dtype)
+    assert np.array_equal(h, H.to_bits(h_ref, dtype))
+    assert np.array_equal(hq, q_ref) and np.array_equal(sx.view(np.uint32), sx_ref.view(np.uint32))
+    assert np.array_equal(xsum, sum_ref)
+    # and it is the product a framework computes, to the last bit of the storage type but for the exponential's ulp
+    import torch
+    t = torch.from_numpy(H.from_bits(gub, dtype)[:, : 2 * f])
+    tdt = {H.BF16: torch.bfloat16, H.F16: torch.float16, H.F32: torch.float32}[dtype]
+    want = (torch.nn.functional.silu(t[:, :f].to(tdt)) * t[:, f:].to(tdt)).float().numpy()
+    got = H.from_bits(h, dtype)
+    ulp = {H.BF16: 2.0 ** -7, H.F16: 2.0 ** -10, H.F32: 2.0 ** -20}[dtype]
+    assert np.all(np.abs(got - want) <= ulp * np.maximum(np.abs(want), 1e-3))
+
+
+@pytest.mark.parametrize("dtype", [H.BF16, H.F32, H.F16])
+@pytest.mark.parametrize("m,d,with_delta", [(1, 2560, True), (3, 70, True), (2, 1, False), (1, 1024, False), (2, 1500, True)])
+def test_add_rmsnorm_quant_kernel(L, oracle, m, d, with_delta, dtype):
+    rng = np.random.default_rng(m * 10 + d + dtype)
+    x = H.to_bits(rng.standard_normal((m, d)).astype(np.float32) * 2.0, dtype)
+    delta = H.to_bits(rng.standard_normal((m, d)).astype(np.float32), dtype) if with_delta else None
+    w = H.to_bits(rng.standard_normal((1, d)).astype(np.float32) * 0.5 + 1.0, dtype)
+    x_before = H.from_bits(x.copy(), dtype)
+    yq, sx, xsum = np.empty((m, d), np.int8), np.empty(m, np.float32), np.empty(m, np.int32)
+    y = H.empty_out((m, d), dtype)
+    H.check(L.bt_add_rmsnorm_quant(H.ptr(x), H.ptr(delta), dtype, m, d, d, d, H.ptr(w), 1e-5, H.ptr(yq), H.ptr(sx),
+                                   H.ptr(xsum), H.ptr(y), None))
+    x_ref, q_ref, sx_ref, sum_ref, y_ref = oracle.add_rmsnorm_quant(
+        x_before, None if delta is None else H.from_bits(delta, dtype), H.from_bits(w, dtype)[0], 1e-5, dtype)
+    assert np.array_equal(x, H.to_bits(x_ref, dtype))             # the residual stream, updated in place
+    assert np.array_equal(y, H.to_bits(y_ref, dtype))
+    assert np.array_equal(yq, q_ref) and np.array_equal(sx.view(np.uint32), sx_ref.view(np.uint32))
+    assert np.array_equal(xsum, sum_ref)
+    # against the framework's RMSNorm on the same rows (its own summation order: the last bit may differ)
+    import torch
+    tdt = {H.BF16: torch.bfloat16, H.F16: torch.float16, H.F32: torch.float32}[dtype]
+    xt = torch.from_numpy(x_ref).to(tdt).float()
+    want = ((xt / torch.sqrt(xt.pow(2).mean(-1, keepdim=True) + 1e-5)) * torch.from_numpy(H.from_bits(w, dtype)[0])).to(tdt).float().numpy()
+    ulp = {H.BF16: 2.0 ** -7, H.F16: 2.0 ** -10, H.F32: 2.0 ** -20}[dtype]
+    assert np.all(np.abs(H.from_bits(y, dtype) - want) <= ulp * np.maximum(np.abs(want), 1e-3))

@@ -11,14 +11,14 @@ pytestmark = pytest.mark.gpu
 VOCAB, DIM, LAYERS, HEADS, FFN, CTX, BATCH = 65, 256, 4, 4, 1024, 128, 8
 
 
-def _models(backend_cuda="cuda", layers=LAYERS):
+def _models(backend_cuda="cuda", layers=LAYERS, fused_elementwise=True):
     """(eager model on the python backend, packed inference model) with identical weights, both on the GPU."""
     from bittorch_b200.utils.decoder import DecoderConfig, TernaryDecoder
 
     torch.manual_seed(0)
     cfg = dict(vocab_size=VOCAB, dim=DIM, n_layers=layers, n_heads=HEADS, ffn_dim=FFN, max_seq_len=CTX)
     eager = TernaryDecoder(DecoderConfig(backend="python", **cfg)).cuda().eval()
-    packed = TernaryDecoder(DecoderConfig(backend=backend_cuda, **cfg)).cuda().eval()
+    packed = TernaryDecoder(DecoderConfig(backend=backend_cuda, fused_elementwise=fused_elementwise, **cfg)).cuda().eval()
     packed.load_state_dict(eager.state_dict())
     packed.to_inference()
     return eager, packed
@@ -73,7 +73,7 @@ def test_every_projection_is_the_oracles_integer_chain(oracle):
     from bittorch_b200.nn import TernaryLinearInference
     from bittorch_b200.utils.decoder import fuse_inference_columns
 
-    _, packed = _models(layers=2)
+    _, packed = _models(layers=2, fused_elementwise=False)     # module by module: the forward hooks see every projection
     calls = []
     hooks = []
 
@@ -217,3 +217,35 @@ def test_inference_form_keeps_one_copy_of_the_weights_and_checkpoints_do_not_cha
     fresh.load_state_dict(torch.load(path))
     with torch.no_grad():
         assert torch.equal(fresh(tokens), want)
+
+
+def test_fused_elementwise_blocks_follow_the_unfused_model():
+    """The inference form with residual add + RMSNorm and SiLU * up inside the quantizer kernels
+    (bt_add_rmsnorm_quant, bt_silu_mul_quant; the kernels themselves are pinned bit for bit elsewhere) against the
+    same model with those steps as framework operations: the two differ only where the framework's own summation
+    order or exponential rounds a value the other way, so logits agree closely, over a prefill, a growing-shape
+    step and a fixed-shape step; fp32 and bf16 models."""
+    from bittorch_b200.utils.decoder import DecoderConfig, TernaryDecoder
+
+    for dtype, tol in ((torch.float32, 2e-3), (torch.bfloat16, 6e-2)):
+        torch.manual_seed(7)
+        cfg = dict(vocab_size=VOCAB, dim=DIM, n_layers=2, n_heads=HEADS, n_kv_heads=2, ffn_dim=FFN, max_seq_len=32)
+        masters = TernaryDecoder(DecoderConfig(backend="python", **cfg)).cuda().eval()
+        models = []
+        for fused in (False, True):
+            m = TernaryDecoder(DecoderConfig(backend="cuda", fused_elementwise=fused, **cfg)).cuda().eval()
+            m.load_state_dict(masters.state_dict())
+            models.append(m.to(dtype).to_inference())
+        plain, fused = models
+        assert fused._fused_blocks() and not plain._fused_blocks()
+        tokens = torch.randint(0, VOCAB, (3, 9), generator=torch.Generator().manual_seed(8)).cuda()
+        with torch.no_grad():
+            ca, cb = plain.new_cache(3), fused.new_cache(3)
+            pairs = [(plain(tokens[:, :7], ca, 0), fused(tokens[:, :7], cb, 0)),
+                     (plain(tokens[:, 7:8], ca, 7), fused(tokens[:, 7:8], cb, 7)),
+                     (plain.decode_step(tokens[:, 8:9], ca, torch.tensor([8], device=tokens.device)),
+                      fused.decode_step(tokens[:, 8:9], cb, torch.tensor([8], device=tokens.device)))]
+        for a, b in pairs:
+            assert a.shape == b.shape
+            rel = float((a.float() - b.float()).norm() / a.float().norm())
+            assert rel < tol, (dtype, rel)

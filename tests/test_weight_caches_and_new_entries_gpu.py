@@ -137,3 +137,33 @@ def test_row_layout_packer_and_unpacker(oracle):
         assert torch.equal(packed.T.contiguous(), bt.quant.pack_ternary_transposed(codes.cuda())[0])
     reserved = torch.full((3, 2), 0xFF, dtype=torch.uint8).cuda()
     assert int(bt.quant.unpack_ternary(reserved, 8).abs().sum()) == 0       # pattern 11 decodes to 0
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32, torch.float16])
+def test_fused_elementwise_kernels_are_the_oracles_arithmetic(oracle, dtype):
+    """bt_silu_mul_quant and bt_add_rmsnorm_quant against their CPU definition, bit for bit: the unquantized values in
+    the activation type, the int8 codes, the scales, the row sums, the residual stream updated in place."""
+    from bittorch_b200 import _C
+
+    code = {torch.float32: oracle.DT_F32, torch.float16: oracle.DT_F16, torch.bfloat16: oracle.DT_BF16}[dtype]
+    g = torch.Generator().manual_seed(31)
+    for m, f in ((1, 6912), (5, 1024), (33, 40), (2, 1)):
+        gu = (torch.randn(m, 2 * f, generator=g) * 4.0).to(dtype)
+        hq, sx, xsum, h = _C.silu_mul_quant(gu.cuda(), want_h=True)
+        q_ref, sx_ref, sum_ref, h_ref = oracle.silu_mul_quant(gu.float().numpy(), code)
+        assert torch.equal(h.cpu(), torch.from_numpy(h_ref).to(dtype))
+        assert np.array_equal(hq.cpu().numpy(), q_ref) and np.array_equal(xsum.cpu().numpy(), sum_ref)
+        assert np.array_equal(sx.cpu().numpy().view(np.uint32), sx_ref.view(np.uint32))
+    for m, d, with_delta in ((1, 2560, True), (4, 256, True), (40, 70, False), (2, 1, True)):
+        x = (torch.randn(m, d, generator=g) * 2.0).to(dtype)
+        delta = torch.randn(m, d, generator=g).to(dtype) if with_delta else None
+        w = (torch.randn(d, generator=g) * 0.5 + 1.0).to(dtype)
+        x_dev = x.clone().cuda()                                                    # updated in place by the kernel
+        yq, sx, xsum, y = _C.add_rmsnorm_quant(x_dev, None if delta is None else delta.cuda(), w.cuda(), 1e-5, want_y=True)
+        x_ref, q_ref, sx_ref, sum_ref, y_ref = oracle.add_rmsnorm_quant(
+            x.float().numpy(), None if delta is None else delta.float().numpy(), w.float().numpy(), 1e-5, code)
+        assert torch.equal(x_dev.cpu(), torch.from_numpy(x_ref).to(dtype))         # in place
+        assert torch.equal(y.cpu(), torch.from_numpy(y_ref).to(dtype))
+        assert np.array_equal(yq.cpu().numpy(), q_ref) and np.array_equal(xsum.cpu().numpy(), sum_ref)
+        assert np.array_equal(sx.cpu().numpy().view(np.uint32), sx_ref.view(np.uint32))
+    assert _C.device_status() == 0
