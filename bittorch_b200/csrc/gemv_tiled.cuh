@@ -637,12 +637,14 @@ static int launch_gemv_tiled_rows(GemvTiledParams p, cudaStream_t st) {
     p.nbl_max = ceil_div(p.NB, grid);
     const int max_tiles = p.nbl_max * p.KT;
     p.stages = std::max(1, std::min(GT_MAX_STAGES, ceil_div(max_tiles, GT_STAGE_TILES)));
+    // 227 KB per CTA, static and dynamic together: leave room for the kernel's few static words
+    constexpr size_t SMEM_LIMIT = 227 * 1024 - 256;
     size_t smem = gemv_tiled_smem(mr, p.KT * TILE_K, p.nbl_max, p.stages);
-    while (smem > 227 * 1024 && p.stages > 1) {               // long rows: a shallower weight ring makes room
+    while (smem > SMEM_LIMIT && p.stages > 1) {               // long rows: a shallower weight ring makes room
         --p.stages;
         smem = gemv_tiled_smem(mr, p.KT * TILE_K, p.nbl_max, p.stages);
     }
-    BT_UNSUPPORTED_IF(smem > 227 * 1024, "gemv_tiled: needs %zu bytes of shared memory (K too large)", smem);
+    BT_UNSUPPORTED_IF(smem > SMEM_LIMIT, "gemv_tiled: needs %zu bytes of shared memory (K too large)", smem);
     if (p.planes) {
         if (mr == 4) return launch_gemv_tiled_kernel<4, GT_ROWS_PLANES>(p, grid, smem, st);
         return launch_gemv_tiled_kernel<8, GT_ROWS_PLANES>(p, grid, smem, st);
