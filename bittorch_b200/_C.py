@@ -56,6 +56,8 @@ _SIGNATURES = {
     "bt_gemv_tiled": ([_p, _int, _i64, _i64, _i64, _p, _i64, _p, _p, _p, _int, _i64, _p, _p, _p, _int, _p], _int),
     "bt_gemv_tiled_chained": ([_p, _int, _i64, _i64, _i64, _p, _i64, _p, _p, _p, _int, _i64, _p, _p, _i64, _int, _p], _int),
     "bt_gemv_tiled_float": ([_p, _int, _i64, _i64, _i64, _p, _i64, _p, _p, _p, _int, _i64, _int, _p], _int),
+    "bt_float_planes_quant": ([_p, _int, _i64, _i64, _i64, _p, _p, _p, _p, _p], _int),
+    "bt_float_planes_combine": ([_p, _i64, _i64, _p, _p, _p, _p, _p, _int, _i64, _p], _int),
     "bt_gemm_tiled_i8": ([_p, _p, _p, _i64, _i64, _p, _i64, _p, _p, _p, _int, _i64, _p, _p], _int),
     "bt_silu_mul_quant": ([_p, _int, _i64, _i64, _i64, _p, _p, _p, _p, _p], _int),
     "bt_add_rmsnorm_quant": ([_p, _p, _int, _i64, _i64, _i64, _i64, _p, _f32, _p, _p, _p, _p, _p], _int),
@@ -391,9 +393,51 @@ def gemv_tiled_float(x2d: Tensor, tiled: Tensor, in_features: int, out_features:
     return y
 
 
+FLOAT_GEMM_ROWS = 1024        # activation rows per tensor-core call of the float path (4096 int8 rows)
+
+
 def float_linear_tiled_ok(m: int, in_features: int, dtype: torch.dtype) -> bool:
-    """Float mode runs the tiled decode kernel for small batches; everything else the general float kernel."""
-    return m <= DECODE_MAX_M and in_features <= FLOAT_GEMV_MAX_K and dtype in _DT
+    """Float mode runs on the tiled weights through the integer kernels (digit planes) when the shape allows:
+    the decode kernel for small batches, the tensor-core GEMM above (K a multiple of 16); otherwise the general
+    float kernel on the public layout."""
+    if in_features > FLOAT_GEMV_MAX_K or dtype not in _DT:
+        return False
+    return m <= DECODE_MAX_M or in_features % 16 == 0
+
+
+def float_linear_tiled(x2d: Tensor, tiled: Tensor, in_features: int, out_features: int, scale: Tensor,
+                       bias: Optional[Tensor], fresh_weights: bool = False) -> Tensor:
+    """Floating-point activations (no activation quantization) on the tiled weights, computed exactly by the
+    integer kernels: ``gemv_tiled_float`` up to DECODE_MAX_M rows; above, digit planes -> tcgen05 GEMM -> combine,
+    FLOAT_GEMM_ROWS activation rows at a time.  Call only when ``float_linear_tiled_ok``."""
+    m = x2d.shape[0]
+    if m <= DECODE_MAX_M:
+        return gemv_tiled_float(x2d, tiled, in_features, out_features, scale, bias, fresh_weights=fresh_weights)
+    if x2d.stride(1) != 1:
+        x2d = x2d.contiguous()
+    dev = x2d.device
+    y = torch.empty((m, out_features), dtype=x2d.dtype, device=dev)
+    rows = min(m, FLOAT_GEMM_ROWS)
+    planes = torch.empty((4 * rows, in_features), dtype=torch.int8, device=dev)
+    pw = torch.empty((rows,), dtype=torch.float32, device=dev)
+    xsum = torch.empty((4 * rows,), dtype=torch.int32, device=dev)
+    bad = torch.empty((rows,), dtype=torch.int32, device=dev)
+    ones = torch.ones((4 * rows,), dtype=torch.float32, device=dev)
+    acc = torch.empty((4 * rows, out_features), dtype=torch.int32, device=dev)
+    scratch = torch.empty((4 * rows, out_features), dtype=torch.bfloat16, device=dev)     # the GEMM's own output, unused
+    with torch.cuda.device(dev):
+        st = _stream(x2d)
+        for m0 in range(0, m, rows):
+            r = min(rows, m - m0)
+            xs = x2d[m0:m0 + r]
+            _check(_lib.bt_float_planes_quant(_ptr(xs), _dtype_code(xs, "X"), r, in_features, xs.stride(0), _ptr(planes),
+                                              _ptr(pw), _ptr(xsum), _ptr(bad), st))
+            _check(_lib.bt_gemm_tiled_i8(_ptr(planes), _ptr(ones), _ptr(xsum), 4 * r, in_features, _ptr(tiled), out_features,
+                                         _ptr(scale), None, _ptr(scratch), BT_BF16, out_features, _ptr(acc), st))
+            ys = y[m0:m0 + r]
+            _check(_lib.bt_float_planes_combine(_ptr(acc), r, out_features, _ptr(pw), _ptr(bad), _ptr(scale), _ptr(bias),
+                                                _ptr(ys), _DT[y.dtype], ys.stride(0), st))
+    return y
 
 
 def new_amax_buffer(layers: int, rows: int, device) -> Tensor:
@@ -596,4 +640,8 @@ def ternary_linear_tensor_core_forward(X: Tensor, W_T: Tensor, scale: Tensor, bi
     if in_features is None:
         in_features = X.shape[-1]
     k, n = _packed_checks(X, W_T, scale, bias, int(in_features))
+    if version == 1 and float_linear_tiled_ok(X.shape[0], k, X.dtype):
+        # float compute on the tensor cores (digit planes); the stateless call re-tiles its weights every time
+        tiled = retile(W_T.contiguous(), k)
+        return float_linear_tiled(X.contiguous(), tiled, k, n, _f32vec(scale), _f32vec(bias), fresh_weights=True)
     return _packed_forward(X, W_T, scale, bias, k, n, "float" if version == 1 else "int8")

@@ -31,6 +31,7 @@
 
 #include "act_quant.cuh"
 #include "common.cuh"
+#include "float_planes.cuh"
 #include "retile.cuh"
 
 namespace bt {
@@ -215,9 +216,7 @@ gemv_tiled_kernel(const GemvTiledParams p) {
             float amax = 0.0f;
 #pragma unroll
             for (int w = 0; w < GT_CONSUMER_WARPS; ++w) amax = fmaxf(amax, s_wmax[w * MR + (row_ok ? m : 0)]);
-            int e = 0;
-            frexpf(amax, &e);                               // amax = f 2^e with f in [0.5, 1): amax < 2^e
-            e = max(-96, min(127, e));                      // rows of denormal size keep a normal scale factor
+            const int e = planes_exponent(amax);            // amax < 2^e
             const float mult = ldexpf(1.0f, 30 - e);
             if (row_ok && j == 0) s_sx[4 * m] = ldexpf(1.0f, e - 30);
             // zero what the planes below will not write: padding rows and the tail past K
@@ -250,15 +249,10 @@ gemv_tiled_kernel(const GemvTiledParams p) {
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
                             if (i >= valid) continue;
-                            int fx = __float2int_rn(__fmul_rn(x[u][i], mult));     // NaN -> 0; the row is flagged
-                            fx = max(-(1 << 30), min(1 << 30, fx));
+                            int b[4];
+                            balanced_digits(planes_fixed_point(x[u][i], mult), b);     // NaN -> 0; the row is flagged
 #pragma unroll
-                            for (int d = 0; d < 3; ++d) {
-                                const int b = static_cast<int>(static_cast<int8_t>(fx & 0xff));   // balanced digit
-                                w[d] |= static_cast<uint32_t>(b & 0xff) << (8 * i);
-                                fx = (fx - b) >> 8;
-                            }
-                            w[3] |= static_cast<uint32_t>(fx & 0xff) << (8 * i);                  // |fx| <= 64 now
+                            for (int d = 0; d < 4; ++d) w[d] |= static_cast<uint32_t>(b[d] & 0xff) << (8 * i);
                         }
                         const bool counted = ((v >> 1) & 3) != 3;      // meets weight planes 0..2 (codes t+1)
 #pragma unroll

@@ -65,6 +65,7 @@ __global__ void wait_timeout_selftest_kernel(int polls) {
 }  // namespace bt
 
 #include "act_quant.cuh"
+#include "float_planes.cuh"
 #include "fused_elementwise.cuh"
 #include "gemm_tcgen05.cuh"
 #include "gemm_tcgen05_2cta.cuh"

@@ -136,7 +136,7 @@ class TernaryLinearCUDAFunction(torch.autograd.Function):
         fresh = fresh or (b32 is not None and b32.data_ptr() != bias.data_ptr())     # a float32 copy made just now
         if C.activation_mode() == "float" or x2d.dtype == torch.float64:      # float64 has no int8 path
             if C.float_linear_tiled_ok(x2d.shape[0], k, x2d.dtype):
-                y2d = C.gemv_tiled_float(x2d, tiled, k, n, scale, b32, fresh_weights=fresh)
+                y2d = C.float_linear_tiled(x2d, tiled, k, n, scale, b32, fresh_weights=fresh)
             else:
                 y2d = C.ternary_linear_packed_forward(x2d, packed_T, scale, b32, k)
         else:

@@ -112,9 +112,9 @@ class TernaryLinearInference(nn.Module):
             raise RuntimeError("X is empty")
         x2d = x.contiguous().reshape(-1, self.in_features)
         if C.activation_mode() == "float" or x.dtype == torch.float64:
-            if C.float_linear_tiled_ok(x2d.shape[0], self.in_features, x.dtype):      # decode: stream the tiled weights
+            if C.float_linear_tiled_ok(x2d.shape[0], self.in_features, x.dtype):      # exact, through the integer kernels
                 tiled, s32, b32, fresh = self._derived()
-                y = C.gemv_tiled_float(x2d, tiled, self.in_features, self.out_features, s32, b32, fresh_weights=fresh)
+                y = C.float_linear_tiled(x2d, tiled, self.in_features, self.out_features, s32, b32, fresh_weights=fresh)
                 return y.reshape(*x.shape[:-1], self.out_features)
             return C.ternary_linear_packed_forward(x, self.public_packed(), self.scale, self.bias, self.in_features)
         tiled, s32, b32, fresh = self._derived()

@@ -256,6 +256,27 @@ int bt_gemv_tiled_float(const void* X, int x_dtype, int64_t M, int64_t K, int64_
                         void* Y, int y_dtype, int64_t ldy, int flags, void* stream);
 
 /*
+ * The same construction around the tensor-core GEMM, for any batch size: the reference's
+ * float-activation kernels for large batches (csrc/kernels/ternary_gemm_production.cu:158-250;
+ * csrc/kernels/ternary_gemm_tensor_core.cu:120-271, "version 1") as three calls,
+ *   bt_float_planes_quant   X [M,K] -> int8 digit planes [4M,K] (row 4m+p = digit p of row m),
+ *                           their int32 row sums xsum [4M], pw float32 [M] (the power of two
+ *                           that undoes the scaling), bad int32 [M] (row holds inf / NaN)
+ *   bt_gemm_tiled_i8        on the planes as 4M int8 rows (sx: any values, e.g. ones), with
+ *                           acc_out int32 [4M,N]
+ *   bt_float_planes_combine acc, pw, bad, scale, bias -> Y [M,N]: the four accumulators of
+ *                           an output recombined in 64 bits, one rounding to float, exact
+ *                           power of two, scale, bias; NaN for flagged rows
+ * giving the correctly rounded exact sum at a quarter of the int8 tensor-core rate.
+ * K <= BT_MAX_K / 2 (and a multiple of 16 for the GEMM); at most 65535 rows per combine call.
+ */
+int bt_float_planes_quant(const void* X, int x_dtype, int64_t M, int64_t K, int64_t ldx,
+                          int8_t* planes, float* pw, int32_t* xsum, int32_t* bad, void* stream);
+int bt_float_planes_combine(const int32_t* acc, int64_t M, int64_t N, const float* pw,
+                            const int32_t* bad, const float* scale, const float* bias,
+                            void* Y, int y_dtype, int64_t ldy, void* stream);
+
+/*
  * Prefill-size packed ternary linear on int8 activations (any M >= 1), same
  * arithmetic as above, contraction on the 5th-generation tensor cores
  * (tcgen05.mma kind::i8, accumulators in tensor memory).  Reads the tiled layout.

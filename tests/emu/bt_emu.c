@@ -448,6 +448,70 @@ int bt_gemv_tiled_float(const void* X, int x_dtype, int64_t M, int64_t K, int64_
     return BT_OK;
 }
 
+int bt_float_planes_quant(const void* X, int x_dtype, int64_t M, int64_t K, int64_t ldx, int8_t* planes, float* pw,
+                          int32_t* xsum, int32_t* bad, void* stream) {
+    (void)stream;
+    REQUIRE(X && planes && pw && xsum && bad, "bt_float_planes_quant: NULL pointer");
+    REQUIRE(valid_dtype(x_dtype), "bt_float_planes_quant: unknown dtype %d", x_dtype);
+    REQUIRE(M > 0 && K > 0, "bt_float_planes_quant: X is empty");
+    REQUIRE(ldx >= K, "bt_float_planes_quant: row stride < K");
+    if (K > BT_MAX_K / 2) return fail(BT_ERR_UNSUPPORTED, "bt_float_planes_quant: K=%lld exceeds %d", (long long)K, BT_MAX_K / 2);
+    float* x = widen(X, x_dtype, M, K, ldx);
+    for (int64_t m = 0; m < M; ++m) {
+        const float* row = x + m * K;
+        float amax = 0.0f;
+        int nonfinite = 0;
+        for (int64_t k = 0; k < K; ++k) {
+            float a = fabsf(row[k]);
+            amax = fmaxf(amax, a);
+            if (!(a <= 3.402823466e38f)) nonfinite = 1;
+        }
+        int e = 0;
+        frexpf(amax, &e);
+        if (e < -96) e = -96;
+        if (e > 127) e = 127;
+        float mult = ldexpf(1.0f, 30 - e);
+        int32_t sums[4] = {0, 0, 0, 0};
+        for (int64_t k = 0; k < K; ++k) {
+            float p = row[k] * mult;
+            int64_t v = (p != p) ? 0 : (int64_t)nearbyintf(p);
+            if (v > (1 << 30)) v = 1 << 30;
+            if (v < -(1 << 30)) v = -(1 << 30);
+            for (int d = 0; d < 4; ++d) {
+                int b = (d < 3) ? (int)(int8_t)(v & 0xff) : (int)v;
+                planes[(4 * m + d) * K + k] = (int8_t)b;
+                sums[d] += b;
+                v = (v - b) >> 8;
+            }
+        }
+        for (int d = 0; d < 4; ++d) xsum[4 * m + d] = sums[d];
+        pw[m] = ldexpf(1.0f, e - 30);
+        bad[m] = nonfinite;
+    }
+    free(x);
+    return BT_OK;
+}
+
+int bt_float_planes_combine(const int32_t* acc, int64_t M, int64_t N, const float* pw, const int32_t* bad, const float* scale,
+                            const float* bias, void* Y, int y_dtype, int64_t ldy, void* stream) {
+    (void)stream;
+    REQUIRE(acc && pw && bad && scale && Y, "bt_float_planes_combine: NULL pointer");
+    REQUIRE(valid_dtype(y_dtype), "bt_float_planes_combine: unknown output dtype %d", y_dtype);
+    REQUIRE(M > 0 && N > 0, "bt_float_planes_combine: empty output");
+    REQUIRE(ldy >= N, "bt_float_planes_combine: output row stride < N");
+    if (M > 65535) return fail(BT_ERR_UNSUPPORTED, "bt_float_planes_combine: more than 65535 rows per call");
+    for (int64_t m = 0; m < M; ++m)
+        for (int64_t n = 0; n < N; ++n) {
+            int64_t total = 0;
+            for (int d = 3; d >= 0; --d) total = total * 256 + acc[(4 * m + d) * N + n];
+            float y = ((float)total * pw[m]) * scale[n];
+            if (bias) y = y + bias[n];
+            if (bad[m]) y = NAN;
+            store_elem(Y, y_dtype, m * ldy + n, y);
+        }
+    return BT_OK;
+}
+
 int bt_gemm_tiled_i8(const int8_t* Xq, const float* sx, const int32_t* xsum, int64_t M, int64_t K, const uint8_t* tiled,
                      int64_t N, const float* scale, const float* bias, void* Y, int y_dtype, int64_t ldy,
                      int32_t* acc_out, void* stream) {

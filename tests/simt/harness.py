@@ -61,6 +61,8 @@ def lib():
             "bt_gemv_tiled_float": [_p, _int, _i64, _i64, _i64, _p, _i64, _p, _p, _p, _int, _i64, _int, _p],
             "bt_linear_unpacked": [_p, _int, _i64, _i64, _p, _i64, _p, _p, _p, _p],
             "bt_linear_packed_float": [_p, _int, _i64, _i64, _p, _i64, _p, _p, _p, _p],
+            "bt_float_planes_quant": [_p, _int, _i64, _i64, _i64, _p, _p, _p, _p, _p],
+            "bt_float_planes_combine": [_p, _i64, _i64, _p, _p, _p, _p, _p, _int, _i64, _p],
             "bt_silu_mul_quant": [_p, _int, _i64, _i64, _i64, _p, _p, _p, _p, _p],
             "bt_add_rmsnorm_quant": [_p, _p, _int, _i64, _i64, _i64, _i64, _p, _f32, _p, _p, _p, _p, _p],
             "bt_device_status": [_p, _p], "simt_set_sm_count": [_int], "simt_take_errors": [ctypes.c_char_p, ctypes.c_size_t],

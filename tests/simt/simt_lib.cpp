@@ -30,6 +30,7 @@ int tuning(int) { return -1; }
 }  // namespace bt
 
 #include "../../bittorch_b200/csrc/act_quant.cuh"
+#include "../../bittorch_b200/csrc/float_planes.cuh"
 #include "../../bittorch_b200/csrc/fused_elementwise.cuh"
 #include "../../bittorch_b200/csrc/gemv_tiled.cuh"
 #include "../../bittorch_b200/csrc/linear_float.cuh"

@@ -349,3 +349,42 @@ def test_add_rmsnorm_quant_kernel(L, oracle, m, d, with_delta, dtype):
     want = ((xt / torch.sqrt(xt.pow(2).mean(-1, keepdim=True) + 1e-5)) * torch.from_numpy(H.from_bits(w, dtype)[0])).to(tdt).float().numpy()
     ulp = {H.BF16: 2.0 ** -7, H.F16: 2.0 ** -10, H.F32: 2.0 ** -20}[dtype]
     assert np.all(np.abs(H.from_bits(y, dtype) - want) <= ulp * np.maximum(np.abs(want), 1e-3))
+
+
+@pytest.mark.parametrize("dtype", [H.F32, H.BF16])
+@pytest.mark.parametrize("m,k,n", [(3, 300, 40), (1, 2100, 16), (5, 16, 300)])
+def test_float_planes_around_an_integer_contraction(L, oracle, m, k, n, dtype):
+    """bt_float_planes_quant -> (an exact integer contraction standing in for the tensor-core GEMM, which subtracts
+    nothing here: weights as -1/0/+1) -> bt_float_planes_combine reproduces the definition of the float path bit for
+    bit: digits are balanced bytes that recompose to the fixed-point value, their row sums are exact, a row with an
+    infinity is flagged and comes out as NaN."""
+    rng = np.random.default_rng(m + k + n + dtype)
+    codes, scale, bias = _weights(rng, n, k)
+    x = rng.standard_normal((m, k)).astype(np.float32) * 10.0 ** rng.integers(-2, 3)
+    if m >= 3:
+        x[1, 5] = np.inf
+        x[2] = 0.0
+    xb = H.to_bits(x, dtype)
+    x32 = H.from_bits(xb, dtype)
+    planes = np.empty((4 * m, k), np.int8)
+    pw, xsum, bad = np.empty(m, np.float32), np.empty(4 * m, np.int32), np.empty(m, np.int32)
+    H.check(L.bt_float_planes_quant(H.ptr(xb), dtype, m, k, k, H.ptr(planes), H.ptr(pw), H.ptr(xsum), H.ptr(bad), None))
+    assert np.array_equal(xsum, planes.astype(np.int32).sum(axis=1))
+    assert np.array_equal(bad != 0, ~np.isfinite(x32).all(axis=1))
+    p = planes.astype(np.int64).reshape(m, 4, k)
+    value = ((p[:, 3] * 256 + p[:, 2]) * 256 + p[:, 1]) * 256 + p[:, 0]
+    assert np.abs(p[:, 3]).max() <= 64
+    for r in range(m):
+        if bad[r]:
+            continue
+        e = max(-96, min(127, int(np.frexp(np.float32(np.abs(x32[r]).max()))[1])))
+        assert np.array_equal(value[r], np.rint(x32[r] * np.float32(2.0 ** (30 - e))).astype(np.int64))
+        assert pw[r] == np.float32(2.0 ** (e - 30))
+    acc = (planes.astype(np.int64) @ codes.astype(np.int64).T).astype(np.int32)            # [4M, N], exact
+    y = H.empty_out((m, n), dtype)
+    H.check(L.bt_float_planes_combine(H.ptr(acc), m, n, H.ptr(pw), H.ptr(bad), H.ptr(scale), H.ptr(bias), H.ptr(y), dtype, n, None))
+    want = _planes_reference(x32, codes, scale, bias)
+    got = H.from_bits(y, dtype)
+    assert np.array_equal(np.isnan(got), np.isnan(want))
+    ok = ~np.isnan(want)
+    assert np.array_equal(H.to_bits(np.where(ok, want, 0), dtype)[ok], y[ok])

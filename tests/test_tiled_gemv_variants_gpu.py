@@ -1,11 +1,14 @@
 """Variants of the tiled decode kernel added after its first GPU runs: the launch flag for freshly written weights,
-chained layers that publish their row maxima, floating-point activations as digit planes.
+chained layers that publish their row maxima, floating-point activations as digit planes (decode kernel, and around
+the tensor-core GEMM: float mode of the modules, which the reference's own float tests exercise).
 (Collected after the files whose tests have already passed on a B200, so that a run that stops at the first failure
 has run those first.)"""
 
 import numpy as np
 import pytest
 import torch
+
+from conftest import golden_cases, load_golden
 
 pytestmark = pytest.mark.gpu
 
@@ -146,3 +149,96 @@ def test_float_mode_of_the_inference_module_streams_the_tiled_weights(oracle, mo
     large = layer(x.cuda())                                                       # general kernel
     assert np.allclose(small.cpu().numpy(), y_ref, rtol=1e-4, atol=1e-4)
     assert np.allclose(large.cpu().numpy(), y_ref, rtol=1e-4, atol=1e-4)
+
+
+def test_float_mode_matches_reference_outputs(monkeypatch):
+    """BITTORCH_B200_ACT=float reproduces the reference's float path at its own 1e-4."""
+    import bittorch_b200 as bt
+
+    monkeypatch.setenv("BITTORCH_B200_ACT", "float")
+    c = load_golden("c1_linear_512x256")
+    layer = bt.nn.TernaryLinear(512, 256, backend="cuda").cuda()
+    with torch.no_grad():
+        layer.weight.copy_(torch.from_numpy(c["w"]))
+        layer.bias.copy_(torch.from_numpy(c["bias"]))
+        y = layer(torch.from_numpy(c["x"]).cuda()).cpu().numpy()
+    assert np.allclose(y, c["y"], rtol=1e-4, atol=1e-4)
+    for name, r in golden_cases(load_golden("ragged_forward")).items():
+        pt = torch.from_numpy(r["packed_T"]).cuda()
+        y = bt.ops.ternary_linear_packed_forward(torch.from_numpy(r["x"]).cuda(), pt, torch.from_numpy(r["scale"]).cuda(),
+                                                 r["x"].shape[1], torch.from_numpy(r["bias"]).cuda())
+        assert np.allclose(y.cpu().numpy(), r["y"], rtol=1e-4, atol=1e-4), name
+        y2 = bt.ops.ternary_linear_forward_cuda(torch.from_numpy(r["x"]).cuda(), torch.from_numpy(r["codes"]).cuda(),
+                                                torch.from_numpy(r["scale"]).cuda(), torch.from_numpy(r["bias"]).cuda())
+        assert np.allclose(y2.cpu().numpy(), r["y"], rtol=1e-4, atol=1e-4), name
+
+
+def test_training_step_gradients_match_python_backend(monkeypatch):
+    """Float mode: forward within 1e-4 of the eager backend and identical STE gradients
+    (tests/test_ternary_linear.py:395-412, tests/test_gradient_consistency.py)."""
+    import bittorch_b200 as bt
+
+    monkeypatch.setenv("BITTORCH_B200_ACT", "float")
+    torch.manual_seed(0)
+    ref = bt.nn.TernaryLinear(64, 48, backend="python").cuda()
+    cu = bt.nn.TernaryLinear(64, 48, backend="cuda").cuda()
+    cu.load_state_dict(ref.state_dict())
+    x = torch.randn(10, 64, device="cuda")
+    x1, x2 = x.clone().requires_grad_(True), x.clone().requires_grad_(True)
+    y1, y2 = ref(x1), cu(x2)
+    assert torch.allclose(y1, y2, rtol=1e-4, atol=1e-5)
+    gy = torch.randn_like(y1)
+    y1.backward(gy)
+    y2.backward(gy)
+    assert torch.allclose(x1.grad, x2.grad, rtol=1e-4, atol=1e-5)
+    assert torch.allclose(ref.weight.grad, cu.weight.grad, rtol=1e-4, atol=1e-5)
+    assert torch.allclose(ref.bias.grad, cu.bias.grad, rtol=1e-4, atol=1e-5)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("m,k,n", [(5, 64, 48), (32, 512, 256), (200, 1024, 640), (1300, 256, 96), (17, 4096, 1024)])
+def test_float_activation_gemm_through_digit_planes(oracle, m, k, n, dtype):
+    """Float mode above the decode sizes: digit planes -> tcgen05 GEMM (4M int8 rows, exact int32 accumulators) ->
+    combine.  Bit-identical to the definition, hence to bt_gemv_tiled_float on the same rows, and within the
+    reference's 1e-4 of the float semantics; 1300 rows go through two GEMM calls."""
+    from bittorch_b200 import _C
+
+    g = torch.Generator().manual_seed(m + k + n)
+    codes = torch.randint(-1, 2, (n, k), generator=g, dtype=torch.int8)
+    x = (torch.randn(m, k, generator=g) * 0.7).to(dtype)
+    scale = torch.rand(n, generator=g) * 0.05 + 0.01
+    bias = torch.randn(n, generator=g)
+    tiled = _C.retile(_C.pack_codes(codes.cuda()), k)
+    torch.cuda.synchronize()
+    assert _C.float_linear_tiled_ok(m, k, dtype)
+    y = _C.float_linear_tiled(x.cuda(), tiled, k, n, scale.cuda(), bias.cuda())
+    torch.cuda.synchronize()
+    assert _C.device_status() == 0
+    want = _planes_definition(x.float().numpy(), codes.numpy(), scale.numpy(), bias.numpy())
+    assert torch.equal(y.cpu(), torch.from_numpy(want).to(dtype))
+    rows = _C.gemv_tiled_float(x[:4].cuda(), tiled, k, n, scale.cuda(), bias.cuda())
+    assert torch.equal(y[:4], rows)
+    y_ref = oracle.linear_float(x.float().numpy(), codes.numpy(), scale.numpy(), bias.numpy())
+    tol = 1e-4 if dtype == torch.float32 else 1e-2
+    assert np.allclose(y.float().cpu().numpy(), y_ref, rtol=tol, atol=tol)
+
+
+def test_tensor_core_forward_versions(oracle):
+    """`ternary_linear_tensor_core_forward` (csrc/kernels/ternary_gemm_tensor_core.cu:663-727): version 1 = float
+    compute (here: exact, on the tensor cores through digit planes), version 2 = int8 activations."""
+    import bittorch_b200 as bt
+
+    g = torch.Generator().manual_seed(21)
+    m, k, n = 48, 256, 160
+    w = torch.randn(n, k, generator=g)
+    codes, scale = oracle.ternarize(w.numpy(), 0.05)
+    packed = torch.from_numpy(oracle.pack_transposed(codes)).cuda()
+    x = torch.randn(m, k, generator=g)
+    bias = torch.randn(n, generator=g)
+    s = torch.from_numpy(scale).cuda()
+    y1 = bt.ops.ternary_linear_tensor_core_forward(x.cuda(), packed, s, k, bias.cuda(), version=1)
+    assert np.allclose(y1.cpu().numpy(), oracle.linear_float(x.numpy(), codes, scale, bias.numpy()), rtol=1e-4, atol=1e-4)
+    y2 = bt.ops.ternary_linear_tensor_core_forward(x.cuda(), packed, s, k, bias.cuda(), version=2)
+    q, sx = oracle.act_quant(x.numpy())
+    y2_ref = oracle.epilogue(oracle.gemm_i32(q, codes), sx, scale, bias.numpy())
+    assert np.array_equal(y2.cpu().numpy().view(np.uint32), y2_ref.view(np.uint32))
