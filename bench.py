@@ -422,10 +422,11 @@ def time_chain(layers, m: int, x0, ranks: Ranks, gather: bool, steps: int, warmu
     return {"ms_per_step": ms_block / steps, "blocks": blocks, "launches_per_step": launches, "graph": graph}
 
 
-def rotating_kernel_us(stack: LayerStack, m: int, reps: int, ranks: Ranks) -> float:
+def rotating_kernel_us(stack: LayerStack, m: int, reps: int, ranks: Ranks, float_activations: bool = False) -> float:
     """Average duration (us) of one linear-layer call over the rotating stack (every call reads the same input, so
     launches are independent): the decode kernel with its quantizer for M <= DECODE_MAX_M, the tensor-core kernel
-    alone (activations quantized beforehand) above."""
+    alone (activations quantized beforehand) above.  `float_activations` (M <= DECODE_MAX_M): the float-activation
+    decode kernel (bt_gemv_tiled_float) instead."""
     from bittorch_b200 import _C
 
     dev = stack.layers[0].tiled.device
@@ -439,7 +440,11 @@ def rotating_kernel_us(stack: LayerStack, m: int, reps: int, ranks: Ranks) -> fl
     def run():
         st = _C._stream(x)
         for l in stack.layers:
-            if m <= _C.DECODE_MAX_M:
+            if float_activations:
+                _C._check(lib.bt_gemv_tiled_float(x.data_ptr(), _C.BT_BF16, m, stack.k, stack.k, l.tiled.data_ptr(), l.n_local,
+                                                  l.scale.data_ptr(), None, y.data_ptr(), _C.BT_BF16, l.n_local,
+                                                  _C.LAUNCH_DEFAULT, st))
+            elif m <= _C.DECODE_MAX_M:
                 launch_linear(l, m, x, stack.k, y, None)
             else:
                 _C._check(lib.bt_gemm_tiled_i8(xq.data_ptr(), sx.data_ptr(), xsum.data_ptr(), m, stack.k,
@@ -698,6 +703,13 @@ def run_single_shape_rooflines(peaks, dev, ranks: Ranks, traffic):
         stack = LayerStack(layers, k, n, dev, seed=k + n + 1)
         us = rotating_kernel_us(stack, 1, 10, ranks)
         out.append(gemv_roofline(us, 1, k, n, peaks, ratio, src, "independent launches over rotating weights"))
+        if (k, n) == (C3["k"], C3["n"]):
+            # the same layer with floating-point activations (four digit planes through the same pipeline)
+            us_f = rotating_kernel_us(stack, 1, 10, ranks, float_activations=True)
+            entry = gemv_roofline(us_f, 1, k, n, peaks, None, None, "float activations (bt_gemv_tiled_float), same weights")
+            entry["kernel"] = "gemv_tiled_kernel<4,planes>"
+            entry["relative_to_int8_path"] = us / us_f
+            out.append(entry)
         del stack
         torch.cuda.empty_cache()
     return out

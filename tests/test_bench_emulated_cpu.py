@@ -39,7 +39,8 @@ def test_one_gpu_line_has_every_contract_key_and_every_leg():
     v = d["chain_variants"]                                     # both chains were timed; the headline is one of them
     assert v["headline"] in ("plain", "published_row_maxima") and v["plain"]["gbs"] > 0 and v["published_row_maxima"]["gbs"] > 0
     assert not [k for k in d if k.endswith("_error")], [d[k] for k in d if k.endswith("_error")]
-    assert len(d["rooflines"]) == 3 and all(x["frac"] > 0 for x in d["rooflines"])
+    assert len(d["rooflines"]) == 4 and all(x["frac"] > 0 for x in d["rooflines"])      # three shapes + the float-activation kernel
+    assert d["rooflines"][1]["kernel"] == "gemv_tiled_kernel<4,planes>" and d["rooflines"][1]["relative_to_int8_path"] > 0
     g = d["roofline_gemm"]
     assert g["bound"] == "tensor" and g["unit"] == "TOP/s" and abs(g["frac"] - g["achieved"] / g["peak"]) < 1e-12
     assert len(d["sweep"]) == 8 and d["config3_stack"]["gbs"] > 0
