@@ -132,3 +132,25 @@ def retile(packed_t: np.ndarray, k: int) -> np.ndarray:
     tiled = raw[off:off + lib().bt_tiled_bytes(k, n)]
     check(lib().bt_retile_packed(ptr(np.ascontiguousarray(packed_t)), k, n, ptr(tiled), None))
     return tiled
+
+
+def planes_reference(x32, codes, scale, bias):
+    """bt_gemv_tiled_float's definition with numpy: 32-bit fixed point from the row maximum's power of two, exact
+    integer contraction, one rounding to float, exact power of two, scale, bias (float32 operations, unfused)."""
+    m = x32.shape[0]
+    y = np.empty((m, codes.shape[0]), np.float32)
+    for r in range(m):
+        row = x32[r]
+        if not np.isfinite(row).all():
+            y[r] = np.nan
+            continue
+        amax = np.float32(np.abs(row).max())
+        e = int(np.frexp(amax)[1])
+        e = max(-96, min(127, e))
+        v = np.rint(row * np.float32(2.0 ** (30 - e))).astype(np.int64)
+        v = np.clip(v, -(1 << 30), 1 << 30)
+        total = codes.astype(np.int64) @ v
+        out = total.astype(np.float32) * np.float32(2.0 ** (e - 30))
+        out = out * scale
+        y[r] = out + bias if bias is not None else out
+    return y
