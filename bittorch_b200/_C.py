@@ -393,7 +393,8 @@ def gemv_tiled_float(x2d: Tensor, tiled: Tensor, in_features: int, out_features:
     return y
 
 
-FLOAT_GEMM_ROWS = 1024        # activation rows per tensor-core call of the float path (4096 int8 rows)
+FLOAT_GEMM_ROWS = 1024        # most activation rows per tensor-core call of the float path (4096 int8 rows)
+FLOAT_GEMM_ACC_BYTES = 256 << 20   # and at most this much int32 accumulator scratch per call
 
 
 def float_linear_tiled_ok(m: int, in_features: int, dtype: torch.dtype) -> bool:
@@ -417,7 +418,7 @@ def float_linear_tiled(x2d: Tensor, tiled: Tensor, in_features: int, out_feature
         x2d = x2d.contiguous()
     dev = x2d.device
     y = torch.empty((m, out_features), dtype=x2d.dtype, device=dev)
-    rows = min(m, FLOAT_GEMM_ROWS)
+    rows = min(m, FLOAT_GEMM_ROWS, max(32, (FLOAT_GEMM_ACC_BYTES // (16 * out_features)) // 32 * 32))
     planes = torch.empty((4 * rows, in_features), dtype=torch.int8, device=dev)
     pw = torch.empty((rows,), dtype=torch.float32, device=dev)
     xsum = torch.empty((4 * rows,), dtype=torch.int32, device=dev)
