@@ -827,6 +827,14 @@ def selftest_published(dev) -> dict:
         chained = make_chain_step(stack.layers, m, x0, ranks, False, True)[0]().clone()
         torch.cuda.synchronize()
         ok = ok and bool(torch.equal(plain.view(torch.int16), chained.view(torch.int16)))
+        del stack
+    # and one block of the headline chain itself: its four shapes, the long-row branch (K = 28672) included
+    block = ProjectionChain(dev, 0, 1, seed=3, c=dict(C5, blocks=2))
+    x0 = torch.randn(1, block.layers[0].k, generator=torch.Generator().manual_seed(9)).to(torch.bfloat16).to(dev)
+    plain = make_chain_step(block.layers, 1, x0, ranks, False, False)[0]().clone()
+    chained = make_chain_step(block.layers, 1, x0, ranks, False, True)[0]().clone()
+    torch.cuda.synchronize()
+    ok = ok and bool(torch.equal(plain.view(torch.int16), chained.view(torch.int16)))
     return {"ok": ok and _C.device_status(dev) == 0}
 
 
