@@ -368,3 +368,31 @@ def test_float_planes_around_an_integer_contraction(L, oracle, m, k, n, dtype):
     assert np.array_equal(np.isnan(got), np.isnan(want))
     ok = ~np.isnan(want)
     assert np.array_equal(H.to_bits(np.where(ok, want, 0), dtype)[ok], y[ok])
+
+
+def test_chained_consumer_with_a_long_row_skips_its_reduction_pass(L, oracle):
+    """A consumer whose rows do not fit the threads' registers (K = 8600 at one row) normally reads them twice
+    (maximum, then quantizer); with the producer's published maximum it reads them once.  Same bits either way."""
+    H.set_sm_count(5)
+    rng = np.random.default_rng(77)
+    shapes = [(200, 8600), (8600, 40)]
+    layers = []
+    for k, n in shapes:
+        codes = rng.integers(-1, 2, (n, k)).astype(np.int8)
+        layers.append((k, n, H.retile(oracle.pack_transposed(codes), k), (rng.random(n) * 0.02 + 0.001).astype(np.float32)))
+    x0 = H.to_bits(rng.standard_normal((1, 200)).astype(np.float32), H.BF16)
+    outs = {}
+    for chained in (False, True):
+        amax = np.zeros((2, 1, 8), np.uint32)
+        x, ldx = x0, 200
+        for i, (k, n, tiled, scale) in enumerate(layers):
+            y = H.empty_out((1, n), H.BF16)
+            if chained:
+                H.check(L.bt_gemv_tiled_chained(H.ptr(x), H.BF16, 1, k, ldx, H.ptr(tiled), n, H.ptr(scale), None, H.ptr(y), H.BF16, n,
+                                                H.ptr(amax[i - 1]) if i > 0 else None, H.ptr(amax[i]), n, 0, None))
+            else:
+                H.check(L.bt_gemv_tiled(H.ptr(x), H.BF16, 1, k, ldx, H.ptr(tiled), n, H.ptr(scale), None, H.ptr(y), H.BF16, n,
+                                        None, None, None, 0, None))
+            x, ldx = y, n
+        outs[chained] = x
+    assert np.array_equal(outs[False], outs[True]) and H.device_status() == 0
