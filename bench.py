@@ -717,6 +717,7 @@ def run_single_shape_rooflines(peaks, dev, ranks: Ranks, traffic):
 
 def _decoder_tools(dev):
     """Helpers of the two tokens/s legs: model builder, event timer, capture hook for the greedy loop."""
+    from bittorch_b200.nn import verify_weight_contents
     from bittorch_b200.utils.decoder import DecoderConfig, TernaryDecoder
 
     def build(vocab, dim, layers, heads, ffn, max_seq, dtype):
@@ -727,6 +728,7 @@ def _decoder_tools(dev):
             model = TernaryDecoder(cfg)
         model = model.to(dtype).eval()
         model.to_inference()                                   # random-init masters -> packed ternary layers
+        verify_weight_contents(model, False)                   # final weights: no host read-back per eager forward
         torch.cuda.empty_cache()
         return model
 

@@ -83,6 +83,24 @@ def usable_cache(cache: Optional[PackedWeightCache]) -> Optional[PackedWeightCac
     return cache
 
 
+def verify_weight_contents(module: nn.Module, enabled: bool) -> int:
+    """Switches the per-forward content check of every ternary layer below ``module`` on or off (the fingerprint
+    behind ``PackedWeightCache.verify`` and ``TernaryLinearInference.verify_buffers``).  Off, a forward compares
+    addresses and version counters only and does not synchronise with the host: for models whose weights are final
+    and whose eager call rate matters.  A later write through ``.data`` then needs ``invalidate_cache()``.
+    Returns the number of layers switched."""
+    switched = 0
+    for m in module.modules():
+        cache = getattr(m, "_cache", None)
+        if isinstance(cache, PackedWeightCache):
+            cache.verify = enabled
+            switched += 1
+        elif hasattr(type(m), "verify_buffers"):
+            m.verify_buffers = enabled
+            switched += 1
+    return switched
+
+
 def _quantized(weight: Tensor, threshold_factor: float, cache: Optional[PackedWeightCache]):
     """(packed_T, tiled, scale float32, fresh): ``fresh`` says that the buffers were written by kernels enqueued just
     now, so the first kernel that reads them must be launched stream-ordered."""

@@ -70,6 +70,41 @@ def test_writes_through_data_are_seen_by_the_cached_paths(oracle):
     assert torch.equal(o1, yb) and torch.equal(o2, m2(x))
 
 
+def test_the_content_check_can_be_switched_off_for_a_whole_model():
+    """`verify_weight_contents(model, False)` reaches the training modules' caches and the inference modules alike;
+    from then on a write through `.data` is seen only after `invalidate_cache()`, and switching the check back on
+    restores the default behaviour."""
+    import bittorch_b200 as bt
+
+    g = torch.Generator().manual_seed(8)
+    k, n = 128, 48
+    w0, w1 = torch.randn(n, k, generator=g).cuda(), torch.randn(n, k, generator=g).cuda()
+    x = torch.randn(2, k, generator=g).cuda()
+    model = torch.nn.Sequential(bt.nn.TernaryLinear(k, n, bias=False, backend="cuda"), bt.nn.TernaryLinearCUDA(k, n, bias=False),
+                                bt.nn.create_ternary_linear_inference(k, n, w0, None)).cuda()
+    assert bt.nn.verify_weight_contents(model, False) == 3
+    with torch.no_grad():
+        for layer in model[:2]:
+            layer.weight.data.copy_(w0)
+            layer.invalidate_cache()
+            y0 = layer(x)
+            layer.weight.data.copy_(w1)
+            assert torch.equal(layer(x), y0)                          # stale by construction
+            layer.invalidate_cache()
+            y1 = layer(x)
+            assert not torch.equal(y1, y0)
+            assert torch.equal(y1, model[2].__class__(k, n, *_packed(bt, w1))(x))
+        assert bt.nn.verify_weight_contents(model, True) == 3
+        model[0].weight.data.copy_(w0)
+        assert torch.equal(model[0](x), y0)                           # seen again without any call
+
+
+def _packed(bt, w):
+    """(weight_packed, scale) of the inference form of master weights `w`."""
+    layer = bt.nn.create_ternary_linear_inference(w.shape[1], w.shape[0], w, None)
+    return layer.weight_packed, layer.scale
+
+
 def test_float64_inputs_run_the_float_path(oracle):
     """The reference dispatches its float kernels for float64 too (AT_DISPATCH_FLOATING_TYPES_AND_HALF) and computes in
     float32 (tests/test_gradient_consistency.py:233-237 feeds float64): same here, through the unpacked entry, the
