@@ -793,7 +793,7 @@ def tokens_config4(dev, ranks: Ranks):
             for b0 in range(0, batch, per_pass):
                 b1 = min(batch, b0 + per_pass)
                 view = [(kc[b0:b1], vc[b0:b1]) for kc, vc in cache]
-                logits = model(prompt[b0:b1], view, 0)
+                logits = model(prompt[b0:b1], view, 0, last_only=True)      # a prefill needs the last position's logits
                 last[b0:b1] = logits[:, -1].argmax(dim=-1, keepdim=True)
 
         prefill()                                              # warm-up (builds the layers' derived buffers)

@@ -367,9 +367,10 @@ class TernaryDecoder(nn.Module):
         shape = (batch, cfg.n_kv_heads, cfg.max_seq_len, cfg.head_dim)
         return [(torch.zeros(shape, dtype=dtype, device=dev), torch.zeros(shape, dtype=dtype, device=dev)) for _ in self.blocks]
 
-    def forward(self, tokens: Tensor, cache: Optional[list] = None, pos0: int = 0) -> Tensor:
+    def forward(self, tokens: Tensor, cache: Optional[list] = None, pos0: int = 0, last_only: bool = False) -> Tensor:
         """tokens: [B, T] ids at positions pos0 .. pos0+T-1 -> logits [B, T, vocab]; ``cache`` (from ``new_cache``)
-        is filled in place; without one the call is a stand-alone pass over the whole sequence."""
+        is filled in place; without one the call is a stand-alone pass over the whole sequence.  ``last_only``: the
+        final norm and the head run on the last position alone -> [B, 1, vocab] (what a prefill needs)."""
         b, t = tokens.shape
         if pos0 + t > self.cfg.max_seq_len:
             raise ValueError(f"positions up to {pos0 + t} exceed max_seq_len={self.cfg.max_seq_len}")
@@ -379,19 +380,21 @@ class TernaryDecoder(nn.Module):
             cache = self.new_cache(b)
         x = self.tok(tokens)
         if self._fused_blocks():
-            return self._run_fused(x, cache, pos0, fixed=False)
+            return self._run_fused(x, cache, pos0, fixed=False, last_only=last_only)
         for block, layer_cache in zip(self.blocks, cache):
             x = block(x, layer_cache, pos0, self.rope_cos, self.rope_sin)
-        return self.head(self.norm(x))
+        return self.head(self.norm(x[:, -1:] if last_only else x))
 
     def _fused_blocks(self) -> bool:
         return len(self.blocks) > 0 and all(block.fused_elementwise_ok() for block in self.blocks)
 
-    def _run_fused(self, x: Tensor, cache: list, pos, fixed: bool) -> Tensor:
+    def _run_fused(self, x: Tensor, cache: list, pos, fixed: bool, last_only: bool = False) -> Tensor:
         x = x.contiguous()                                     # the embedding's output: a fresh tensor, updated in place
         delta = None
         for block, layer_cache in zip(self.blocks, cache):
             x, delta = block.forward_fused(x, delta, layer_cache, pos, self.rope_cos, self.rope_sin, fixed)
+        if last_only:
+            x, delta = x[:, -1:], delta[:, -1:]
         return self.head(self.norm(x + delta))
 
     def decode_step(self, tokens: Tensor, cache: list, pos: Tensor) -> Tensor:
@@ -410,7 +413,7 @@ class TernaryDecoder(nn.Module):
         b, t = prompt.shape
         cache = self.new_cache(b)
         out = [prompt]
-        nxt = self.forward(prompt, cache, 0)[:, -1].argmax(dim=-1, keepdim=True)
+        nxt = self.forward(prompt, cache, 0, last_only=True)[:, -1].argmax(dim=-1, keepdim=True)
         for i in range(new_tokens):
             out.append(nxt)
             if i + 1 < new_tokens:

@@ -67,7 +67,9 @@ def test_decoding_against_the_cache_equals_recomputing_the_sequence(n_kv_heads):
         cache = model.new_cache(2)
         pre = model(tokens[:, :6], cache, 0)                   # prefill six, then four single-token steps
         steps = [model(tokens[:, 6 + i:7 + i], cache, 6 + i) for i in range(4)]
+        last = model(tokens[:, :6], model.new_cache(2), 0, last_only=True)
     assert torch.allclose(pre, full[:, :6], atol=1e-5)
+    assert last.shape == (2, 1, 65) and torch.allclose(last, pre[:, -1:], atol=1e-5)     # a prefill's logits: the last position alone
     for i, s in enumerate(steps):
         assert torch.allclose(s[:, 0], full[:, 6 + i], atol=1e-5)
 

@@ -245,6 +245,12 @@ def test_fused_elementwise_blocks_follow_the_unfused_model():
                      (plain(tokens[:, 7:8], ca, 7), fused(tokens[:, 7:8], cb, 7)),
                      (plain.decode_step(tokens[:, 8:9], ca, torch.tensor([8], device=tokens.device)),
                       fused.decode_step(tokens[:, 8:9], cb, torch.tensor([8], device=tokens.device)))]
+            # a prefill that asks for the last position only gets the same logits for it (the head's matrix product
+            # over one row instead of seven may round its sums in another order)
+            for m, full in ((plain, pairs[0][0]), (fused, pairs[0][1])):
+                last = m(tokens[:, :7], m.new_cache(3), 0, last_only=True)
+                assert last.shape == full[:, -1:].shape
+                assert float((last.float() - full[:, -1:].float()).norm() / full[:, -1:].float().norm()) < tol / 10
         for a, b in pairs:
             assert a.shape == b.shape
             rel = float((a.float() - b.float()).norm() / a.float().norm())
