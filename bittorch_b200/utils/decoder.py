@@ -229,12 +229,17 @@ class Attention(nn.Module):
         v_cache[:, :, pos0:pos0 + t] = v.to(v_cache.dtype)
         keys = k_cache[:, :, :pos0 + t].to(q.dtype)
         vals = v_cache[:, :, :pos0 + t].to(q.dtype)
-        if nkv != nh:
-            keys = keys.repeat_interleave(nh // nkv, dim=1)                      # query head h reads kv head h // group
-            vals = vals.repeat_interleave(nh // nkv, dim=1)
-        # query at position pos0 + i sees keys 0 .. pos0 + i
-        mask = torch.ones(t, pos0 + t, dtype=torch.bool, device=q.device).tril(diagonal=pos0)
-        out = F.scaled_dot_product_attention(q, keys, vals, attn_mask=mask, scale=1.0 / math.sqrt(hd))
+        # query at position pos0 + i sees keys 0 .. pos0 + i; query head h reads key/value head h // group
+        # (enable_gqa).  The two common cases need no mask tensor: a pass from position 0 is plain causal
+        # attention, a single token sees every key there is.
+        if t == 1:
+            mask, causal = None, False
+        elif pos0 == 0:
+            mask, causal = None, True
+        else:
+            mask, causal = torch.ones(t, pos0 + t, dtype=torch.bool, device=q.device).tril(diagonal=pos0), False
+        out = F.scaled_dot_product_attention(q, keys, vals, attn_mask=mask, is_causal=causal, scale=1.0 / math.sqrt(hd),
+                                             enable_gqa=nkv != nh)
         return out.transpose(1, 2).reshape(b, t, cfg.dim)
 
     def _attend_fixed(self, q: Tensor, k: Tensor, v: Tensor, cache: Tuple[Tensor, Tensor], pos: Tensor, cos: Tensor,
