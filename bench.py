@@ -422,30 +422,40 @@ def time_chain(layers, m: int, x0, ranks: Ranks, gather: bool, steps: int, warmu
     return {"ms_per_step": ms_block / steps, "blocks": blocks, "launches_per_step": launches, "graph": graph}
 
 
-def rotating_kernel_us(stack: LayerStack, m: int, reps: int, ranks: Ranks, float_activations: bool = False) -> float:
+def rotating_kernel_us(stack: LayerStack, m: int, reps: int, ranks: Ranks, float_activations: bool = False,
+                       path: str = None) -> float:
     """Average duration (us) of one linear-layer call over the rotating stack (every call reads the same input, so
-    launches are independent): the decode kernel with its quantizer for M <= DECODE_MAX_M, the tensor-core kernel
-    alone (activations quantized beforehand) above.  `float_activations` (M <= DECODE_MAX_M): the float-activation
-    decode kernel (bt_gemv_tiled_float) instead."""
+    launches are independent).  `path`: "fused" = the decode kernel with its quantizer inside (bt_gemv_tiled),
+    "int8_rows" = the decode kernel on rows quantized beforehand (bt_gemv_tiled_i8), "tensor_core" = the tcgen05
+    kernel on rows quantized beforehand (bt_gemm_tiled_i8), "float" = the float-activation decode kernel
+    (bt_gemv_tiled_float).  Default: what the modules run, "fused" up to DECODE_MAX_M rows and "tensor_core" above."""
     from bittorch_b200 import _C
 
+    if path is None:
+        path = "float" if float_activations else ("fused" if m <= _C.DECODE_MAX_M else "tensor_core")
     dev = stack.layers[0].tiled.device
     g = torch.Generator(device=dev).manual_seed(1)
     x = torch.randn(m, stack.k, generator=g, device=dev).to(torch.bfloat16)
     y = torch.empty((m, stack.n_local), dtype=torch.bfloat16, device=dev)
     lib = _C._lib
-    if m > _C.DECODE_MAX_M:
+    if path in ("int8_rows", "tensor_core"):
         xq, sx, xsum = _C.act_quant_i8(x, want_sum=True)
 
     def run():
         st = _C._stream(x)
         for l in stack.layers:
-            if float_activations:
+            if path == "float":
                 _C._check(lib.bt_gemv_tiled_float(x.data_ptr(), _C.BT_BF16, m, stack.k, stack.k, l.tiled.data_ptr(), l.n_local,
                                                   l.scale.data_ptr(), None, y.data_ptr(), _C.BT_BF16, l.n_local,
                                                   _C.LAUNCH_DEFAULT, st))
-            elif m <= _C.DECODE_MAX_M:
-                launch_linear(l, m, x, stack.k, y, None)
+            elif path == "fused":
+                _C._check(lib.bt_gemv_tiled(x.data_ptr(), _C.BT_BF16, m, stack.k, stack.k, l.tiled.data_ptr(), l.n_local,
+                                            l.scale.data_ptr(), None, y.data_ptr(), _C.BT_BF16, l.n_local,
+                                            None, None, None, _C.LAUNCH_DEFAULT, st))
+            elif path == "int8_rows":
+                _C._check(lib.bt_gemv_tiled_i8(xq.data_ptr(), sx.data_ptr(), m, stack.k, l.tiled.data_ptr(), l.n_local,
+                                               l.scale.data_ptr(), None, y.data_ptr(), _C.BT_BF16, l.n_local, None,
+                                               _C.LAUNCH_DEFAULT, st))
             else:
                 _C._check(lib.bt_gemm_tiled_i8(xq.data_ptr(), sx.data_ptr(), xsum.data_ptr(), m, stack.k,
                                                l.tiled.data_ptr(), l.n_local, l.scale.data_ptr(), None, y.data_ptr(),
@@ -456,6 +466,27 @@ def rotating_kernel_us(stack: LayerStack, m: int, reps: int, ranks: Ranks, float
     ms, _ = time_blocks(graph.replay, reps, 3, ranks)
     graph.reset()
     return ms * 1e3 / (reps * len(stack.layers))
+
+
+def act_quant_us(m: int, k: int, reps: int, ranks: Ranks, dev) -> float:
+    """Average duration (us) of the stand-alone activation quantizer on [m, k] bf16 rows (32 calls per replay)."""
+    from bittorch_b200 import _C
+
+    x = torch.randn(m, k, generator=torch.Generator(device=dev).manual_seed(2), device=dev).to(torch.bfloat16)
+    xq = torch.empty((m, k), dtype=torch.int8, device=dev)
+    sx = torch.empty((m,), dtype=torch.float32, device=dev)
+    xsum = torch.empty((m,), dtype=torch.int32, device=dev)
+    calls = 32
+
+    def run():
+        st = _C._stream(x)
+        for _ in range(calls):
+            _C._check(_C._lib.bt_act_quant_i8(x.data_ptr(), _C.BT_BF16, m, k, k, xq.data_ptr(), sx.data_ptr(), xsum.data_ptr(), st))
+
+    graph, _ = capture(run)
+    ms, _ = time_blocks(graph.replay, reps, 3, ranks)
+    graph.reset()
+    return ms * 1e3 / (reps * calls)
 
 
 # ---------------------------------------------------------------------------------------
@@ -715,6 +746,43 @@ def run_single_shape_rooflines(peaks, dev, ranks: Ranks, traffic):
     return out
 
 
+def run_decode_batch_paths(peaks, dev, ranks: Ranks):
+    """Where a small batch should run: for M = 1 .. 32 rows on two layer shapes, the kernel-only time of the decode
+    kernel with its quantizer inside, the decode kernel on int8 rows (plus the stand-alone quantizer, which fused
+    elementwise producers make unnecessary) and the tensor-core kernel on int8 rows, weights rotated past L2.  The
+    table is what the DECODE_MAX_M switch-over of the modules rests on."""
+    from bittorch_b200 import _C
+
+    out = {"decode_max_m_in_use": _C.DECODE_MAX_M, "shapes": []}
+    for k, n in ((C3["k"], C3["n"]), (C5["hidden"], C5["ffn"])):
+        layers = max(4, int(math.ceil(ROTATE_BYTES / (k // 4 * n))))
+        stack = LayerStack(layers, k, n, dev, seed=k + n + 2)
+        rows = []
+        for m in (1, 2, 4, 8, 16, 32):
+            row = {"M": m, "act_quant_us": act_quant_us(m, k, 10, ranks, dev)}
+            for path in ("fused", "int8_rows", "tensor_core"):
+                if (path == "tensor_core" and m < 4) or (path != "tensor_core" and m > _C.GEMV_MAX_M):
+                    continue
+                try:
+                    us = rotating_kernel_us(stack, m, 10, ranks, path=path)
+                    row[path + "_us"] = us
+                    row[path + "_frac_hbm_measured"] = algorithmic_bytes(m, k, n) / us / 1e3 / peaks["hbm_gbs"]
+                except Exception as exc:      # noqa: BLE001  (a refused shape costs its cell only)
+                    row[path + "_error"] = f"{type(exc).__name__}: {exc}"[:200]
+                    torch.cuda.synchronize()
+            # all-in cost from floating-point rows / from int8 rows a fused producer already wrote
+            from_float = {p_: row[p_ + "_us"] + (0.0 if p_ == "fused" else row["act_quant_us"])
+                          for p_ in ("fused", "int8_rows", "tensor_core") if p_ + "_us" in row}
+            from_int8 = {p_: row[p_ + "_us"] for p_ in ("int8_rows", "tensor_core") if p_ + "_us" in row}
+            row["fastest_from_float_rows"] = min(from_float, key=from_float.get) if from_float else None
+            row["fastest_from_int8_rows"] = min(from_int8, key=from_int8.get) if from_int8 else None
+            rows.append(row)
+        out["shapes"].append({"K": k, "N": n, "rows": rows})
+        del stack
+        torch.cuda.empty_cache()
+    return out
+
+
 def _decoder_tools(dev):
     """Helpers of the two tokens/s legs: model builder, event timer, capture hook for the greedy loop."""
     from bittorch_b200.nn import verify_weight_contents
@@ -840,7 +908,7 @@ def selftest_published(dev) -> dict:
     return {"ok": ok and _C.device_status(dev) == 0}
 
 
-LEGS = ("rooflines", "config3", "tokens_config2", "tokens_config4")
+LEGS = ("rooflines", "config3", "decode_batch_paths", "tokens_config2", "tokens_config4")
 
 
 def run_leg(name: str, dev, ranks: Ranks):
@@ -850,6 +918,8 @@ def run_leg(name: str, dev, ranks: Ranks):
         return run_single_shape_rooflines(peaks, dev, ranks, traffic)
     if name == "config3":
         return run_config3(peaks, dev, ranks, traffic)
+    if name == "decode_batch_paths":
+        return run_decode_batch_paths(peaks, dev, ranks)
     if name == "selftest_published":
         return selftest_published(dev)
     if name == "tokens_config2":

@@ -44,6 +44,17 @@ def test_one_gpu_line_has_every_contract_key_and_every_leg():
     g = d["roofline_gemm"]
     assert g["bound"] == "tensor" and g["unit"] == "TOP/s" and abs(g["frac"] - g["achieved"] / g["peak"]) < 1e-12
     assert len(d["sweep"]) == 8 and d["config3_stack"]["gbs"] > 0
+    paths = d["decode_batch_paths"]                             # the table the decode / tensor-core switch-over rests on
+    assert paths["decode_max_m_in_use"] >= 1 and len(paths["shapes"]) == 2
+    for shape in paths["shapes"]:
+        assert [r["M"] for r in shape["rows"]] == [1, 2, 4, 8, 16, 32]
+        for r in shape["rows"]:
+            assert not [k for k in r if k.endswith("_error")], r
+            assert r["act_quant_us"] > 0
+            assert ("fused_us" in r) == ("int8_rows_us" in r) == (r["M"] <= 16)      # the decode entries take 16 rows
+            assert ("tensor_core_us" in r) == (r["M"] >= 4)
+            assert r["fastest_from_float_rows"] in ("fused", "int8_rows", "tensor_core")
+            assert r["fastest_from_int8_rows"] in ("int8_rows", "tensor_core")
     t = d["tokens_per_s"]
     assert t["config2"]["decode_tokens_per_s"] > 0
     assert [r["batch"] for r in t["config4"]["rows"]] == [1, 3]
