@@ -959,8 +959,8 @@ def run_case(case: str, m, k, n) -> None:
     kernel is bandwidth-bound, well under 1 GB on the device."""
     from bittorch_b200 import _C
 
-    dev = torch.device("cuda", 0)
-    torch.cuda.set_device(dev)
+    dev = device_of(0)
+    torch.cuda.set_device(0)
     k = k or C3["k"]
     n = n or C3["n"]
     if case in ("gemv", "gemm"):

@@ -78,3 +78,10 @@ def test_two_rank_line_is_the_same_job_sharded_with_gathers():
     # the headline is the M = 1 sharded chain with its gathers
     assert abs(rows[0]["us_per_block_sharded"] * 2 / 1e3 - d["ms_per_step"]) < 1e-9
     assert d["roofline"]["algorithmic_bytes_per_launch"] < 40576             # a rank streams its shard only
+
+
+def test_the_profiling_cases_run():
+    """`bench.py --case ...` is the program the profiler captures: each case runs its few launches and reports."""
+    for case in ("gemv", "gemm", "quantize", "actquant"):
+        d = _line([sys.executable, RUNNER, "--case", case, "--case-m", "4", "--case-k", "256", "--case-n", "512"], timeout=300)
+        assert d == {"case": case, "m": 4, "k": 256, "n": 512, "device_status": 0}
