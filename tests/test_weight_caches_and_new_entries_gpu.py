@@ -202,3 +202,15 @@ def test_fused_elementwise_kernels_are_the_oracles_arithmetic(oracle, dtype):
         assert np.array_equal(yq.cpu().numpy(), q_ref) and np.array_equal(xsum.cpu().numpy(), sum_ref)
         assert np.array_equal(sx.cpu().numpy().view(np.uint32), sx_ref.view(np.uint32))
     assert _C.device_status() == 0
+
+
+def test_the_smoke_entry_point_and_its_report_of_the_newer_paths(monkeypatch):
+    """`__graft_entry__.smoke()` passes, and what its child process would report about the newer entry points (here
+    computed in this process) is all true with a clean device status."""
+    import __graft_entry__ as entry
+
+    monkeypatch.setattr(entry, "_report_newer_paths", lambda: None)
+    entry.smoke()
+    report = entry.newer_paths()["newer_paths"]
+    assert report.pop("device_status") == 0
+    assert report and all(v is True for v in report.values()), report
